@@ -1,0 +1,482 @@
+#!/usr/bin/env python
+"""Benchmark of the CSR x dense SpMM hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--kernel auto|row|merge|tma]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+    python bench.py --impl reference ...        # the CPU arm (see below)
+
+One step = one SpMM (C = A*B, alpha 1, beta 0) over the whole workload.  The default workload is
+BASELINE config 5 ("cfg5_xl": 2^22 x 2^22, Zipf(2.2) row lengths with mean 32, B 2^22 x 512), the
+configuration the 1/2/4/8-GPU metric is defined on; it fits one GPU.  With N > 1 the rows of A
+and C are split into N contiguous blocks of equal (nnz + rows), B is broadcast once over NCCL
+outside the timed region, and every rank multiplies its block: strong scaling, no collective in
+the timed loop.  Rank 0 prints ONE JSON line.
+
+  value / ms_per_step   device time, max over ranks, inputs resident in HBM
+  e2e                   the same product through csrspmm_b200_spmm_host: pinned HOST buffers in,
+                        host C out, copies inside the timed region
+  roofline              compulsory bytes of rank 0's block / its step time, against the measured
+                        HBM copy bandwidth in MEASURED_PEAKS.json
+  cpu_baseline          the CPU oracle (OpenMP over rows) on a bounded row sample, rank 0, N = 1
+  other_workloads       N = 1 only: the other BASELINE configs (kernel time, roofline, cuSPARSE via
+                        torch.sparse) measured after the main loop
+
+--impl reference times the CPU restatement of the reference's arithmetic (the reference ships no
+host SpMM; see oracle/spmm_oracle.c) on all host threads over a bounded row sample of the same
+workload and prints the same line with "impl": "reference".
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+L2_BYTES = 126 * 2 ** 20
+FALLBACK_HBM_GBS = 6650.0
+
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu
+# captures summarised under profiles/ (bytes; None = not captured yet)
+NCU_TRAFFIC = {}
+
+
+def measured_peak():
+    f = ROOT / "MEASURED_PEAKS.json"
+    if f.exists():
+        try:
+            return float(json.loads(f.read_text())["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return FALLBACK_HBM_GBS, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU through NVML while a region runs
+    (read-only queries)."""
+
+    def __init__(self, index: int, period_s: float = 0.05):
+        self.index, self.period = index, period_s
+        self.samples, self.reasons = [], set()
+        self.max_mhz = None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = int(pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM))
+        except Exception:
+            self.nv = None
+
+    _NAMES = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap",
+              0x80: "hw_power_brake_slowdown"}
+
+    def _loop(self):
+        nv = self.nv
+        while not self._stop.is_set():
+            try:
+                self.samples.append(int(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM)))
+                try:
+                    mask = int(nv.nvmlDeviceGetCurrentClocksEventReasons(self.h))
+                except Exception:
+                    mask = int(nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h))
+                for bit, name in self._NAMES.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            self._stop.wait(self.period)
+
+    def __enter__(self):
+        if self.nv is not None:
+            self._thread = threading.Thread(target=self._loop, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join()
+
+    def summary(self):
+        return {"sm_mhz": float(np.median(self.samples)) if self.samples else None, "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+def physical_gpu_index(local_index: int) -> int:
+    vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+    if vis:
+        try:
+            return int(vis.split(",")[local_index])
+        except Exception:
+            return local_index
+    return local_index
+
+
+# ---------------------------------------------------------------------------------------------------
+
+def time_spmm(torch, ops, t, C_out, workspace, kernel, steps, warmup, flush_buf, max_row_nnz=0, e2m1=None):
+    """Runs warmup + steps SpMMs; returns seconds per step on this device."""
+    kw = dict(kernel=kernel, workspace=workspace, max_row_nnz=max_row_nnz)
+    if e2m1 is not None:
+        kw.update(e2m1_scale=e2m1[1], nnz=e2m1[2])
+    vals = e2m1[0] if e2m1 is not None else t["values"]
+    # argument block prepared once: a step is one call through the C ABI
+    step = ops.SpmmCall(t["row_ptr"], t["col_idx"], vals, t["B"], C_out, 1.0, 0.0, **kw)
+
+    for _ in range(warmup):
+        if flush_buf is not None:
+            flush_buf.zero_()
+        step()
+    torch.cuda.synchronize()
+    starts = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+    stops = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+    for i in range(steps):
+        if flush_buf is not None:
+            flush_buf.zero_()  # evicts the previous step's lines from L2
+        starts[i].record()
+        step()
+        stops[i].record()
+    torch.cuda.synchronize()
+    if flush_buf is None:
+        total_ms = starts[0].elapsed_time(stops[-1])  # back to back, launch gaps included
+    else:
+        total_ms = sum(s.elapsed_time(e) for s, e in zip(starts, stops))
+    return total_ms / 1e3 / steps
+
+
+def problem_bytes(G, t, M, Nd, nnz, Kd, value_bytes=4.0):
+    touched = G.touched_rows(t["col_idx"], Kd) if nnz else 0
+    return G.min_bytes(M, Nd, nnz, touched, 0.0, value_bytes), touched
+
+
+def cusparse_via_torch(torch, t, M, Kd, steps, warmup, flush_buf):
+    """cuSPARSE CSR SpMM as torch.sparse dispatches it (comparator only)."""
+    try:
+        A = torch.sparse_csr_tensor(t["row_ptr"], t["col_idx"], t["values"], size=(M, Kd))
+        for _ in range(max(warmup, 1)):
+            out = torch.sparse.mm(A, t["B"])
+        torch.cuda.synchronize()
+        starts = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+        stops = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+        for i in range(steps):
+            if flush_buf is not None:
+                flush_buf.zero_()
+            starts[i].record()
+            out = torch.sparse.mm(A, t["B"])
+            stops[i].record()
+        torch.cuda.synchronize()
+        del out
+        return sum(s.elapsed_time(e) for s, e in zip(starts, stops)) / 1e3 / steps
+    except Exception as e:  # comparator is best effort
+        return f"unavailable: {type(e).__name__}: {e}"[:200]
+
+
+def cpu_sample(torch, G, oracle, prob, sample_rows, threads, repeats=2):
+    """Times the CPU oracle on rows [0, sample_rows) of the problem (B complete, on the host)."""
+    rp = prob.row_ptr[: sample_rows + 1]
+    rp_h = (rp.cpu().numpy() if hasattr(rp, "cpu") else np.asarray(rp)).astype(np.int32)
+    n = int(rp_h[-1])
+    to_h = (lambda x: x.cpu().numpy()) if hasattr(prob.col_idx, "cpu") else np.asarray
+    ci_h, va_h = to_h(prob.col_idx[:n]), to_h(prob.values[:n])
+    B_h = to_h(prob.B)
+    best = float("inf")
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        oracle.spmm(rp_h, ci_h, va_h, B_h, threads=threads)
+        best = min(best, time.perf_counter() - t0)
+    return 2.0 * n * prob.Nd / best / 1e9, n, best
+
+
+def sample_rows_for(name, M):
+    # sized for roughly 10-30 s of CPU work on a few dozen cores
+    return {"cfg5_xl": M // 16, "cfg3_powerlaw": M // 2, "cfg4_fp4": M // 4}.get(name, M)
+
+
+# ---------------------------------------------------------------------------------------------------
+
+def run_reference_arm(ns):
+    import torch
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return 0
+    import oracle
+    from csrspmm_b200 import generators as G
+    device = "cuda" if torch.cuda.is_available() else "cpu"
+    prob = G.make(ns.workload, scale=ns.scale, device=device)
+    threads = oracle.max_threads()
+    rows = sample_rows_for(ns.workload, prob.M)
+    # untimed warm-up pass(es), then K timed passes over the sample
+    times = []
+    rp_h = (prob.row_ptr[: rows + 1].cpu().numpy() if hasattr(prob.row_ptr, "cpu") else prob.row_ptr[: rows + 1]).astype(np.int32)
+    n = int(rp_h[-1])
+    to_h = (lambda x: x.cpu().numpy()) if hasattr(prob.col_idx, "cpu") else np.asarray
+    ci_h, va_h, B_h = to_h(prob.col_idx[:n]), to_h(prob.values[:n]), to_h(prob.B)
+    for i in range(ns.warmup + ns.steps):
+        t0 = time.perf_counter()
+        oracle.spmm(rp_h, ci_h, va_h, B_h, threads=threads)
+        if i >= ns.warmup:
+            times.append(time.perf_counter() - t0)
+    sec = float(np.mean(times))
+    gflops = 2.0 * n * prob.Nd / sec / 1e9
+    sample = f"rows [0, {rows}) of {prob.M} ({n} of {prob.nnz} nnz), B complete on the host"
+    line = {
+        "impl": "reference", "metric": "SpMM GFLOPS", "value": gflops, "unit": "GFLOPS", "n_gpus": ns.gpus,
+        "steps": ns.steps, "warmup": ns.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": prob.name, "M": prob.M, "Kd": prob.Kd, "Nd": prob.Nd, "nnz": prob.nnz,
+                   "note": "CPU restatement of the reference kernels' arithmetic (the reference has no host SpMM), "
+                           "OpenMP over rows, one step = one pass over the row sample"},
+        "cpu_baseline": {"value": gflops, "unit": "GFLOPS", "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": gflops, "unit": "GFLOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+    return 0
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="cfg5_xl")
+    ap.add_argument("--scale", type=int, default=1, help="divide M and Kd (for quick runs and ncu captures)")
+    ap.add_argument("--kernel", default="auto", choices=["auto", "row", "merge", "tma"])
+    ap.add_argument("--no-extras", action="store_true", help="skip e2e, cpu_baseline and other_workloads")
+    ap.add_argument("--e2e-steps", type=int, default=3)
+    ns = ap.parse_args(argv)
+    ns.warmup = max(ns.warmup, 3) if ns.impl == "ours" else ns.warmup
+
+    if ns.impl == "reference":
+        return run_reference_arm(ns)
+
+    import torch
+    import torch.distributed as dist
+    from csrspmm_b200 import _lib, distributed as D, generators as G, ops
+
+    _lib.lib()  # fail here, loudly, when the CUDA library is missing
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback)")
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != ns.gpus:
+        raise SystemExit(f"--gpus {ns.gpus} but WORLD_SIZE={world}: launch one rank per GPU with torch.distributed.run")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    # ---- the workload: generated on rank 0's GPU, replicated once (untimed) ------------------------
+    cfg = G.CONFIGS[ns.workload]
+    if rank == 0:
+        prob = G.make(ns.workload, scale=ns.scale, device=dev)
+        sizes = torch.tensor([prob.M, prob.Kd, prob.Nd, prob.nnz], dtype=torch.int64, device=dev)
+    else:
+        prob, sizes = None, torch.zeros(4, dtype=torch.int64, device=dev)
+    if world > 1:
+        dist.broadcast(sizes, 0)
+    M, Kd, Nd, nnz = (int(x) for x in sizes.tolist())
+    if rank == 0:
+        row_ptr, col_idx, values, B = prob.row_ptr, prob.col_idx, prob.values, prob.B
+    else:
+        row_ptr = torch.empty(M + 1, dtype=torch.int32, device=dev)
+        col_idx = torch.empty(nnz, dtype=torch.int32, device=dev)
+        values = torch.empty(nnz, dtype=torch.float32, device=dev)
+        B = torch.empty((Kd, Nd), dtype=torch.float32, device=dev)
+    t_bcast = 0.0
+    if world > 1:
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for x in (row_ptr, col_idx, values, B):
+            D.replicate(x, 0)
+        torch.cuda.synchronize()
+        t_bcast = time.perf_counter() - t0
+
+    # ---- nnz-balanced row partition (host), this rank's block -----------------------------------
+    rp_host = row_ptr.cpu().numpy()
+    bounds = D.partition_rows(rp_host, world, 1.0)
+    imbalance = D.partition_imbalance(rp_host, bounds, 1.0)
+    shard = D.take_shard(row_ptr, col_idx, values, bounds, rank)
+    t = {"row_ptr": shard.row_ptr, "col_idx": shard.col_idx, "values": shard.values, "B": B}
+    if world > 1:
+        del row_ptr, col_idx, values
+    my_rows, my_nnz = shard.rows, shard.nnz
+    C_out = torch.empty((my_rows, Nd), dtype=torch.float32, device=dev)
+    workspace = torch.empty(max(ops.workspace_bytes(my_rows, Kd, Nd, my_nnz), 256), dtype=torch.uint8, device=dev)
+    my_bytes, touched = problem_bytes(G, t, my_rows, Nd, my_nnz, Kd)
+    footprint = my_nnz * 8 + my_rows * 4 + (Kd + my_rows) * Nd * 4
+    flush = footprint < 2 * L2_BYTES
+    flush_buf = torch.empty(2 * L2_BYTES, dtype=torch.uint8, device=dev) if flush else None
+    chosen = ops.selected_kernel(my_rows, Kd, Nd, my_nnz, kernel=ns.kernel, max_row_nnz=0)
+    launches_per_step = 1 if chosen == "row" else 2
+
+    # ---- timed region -------------------------------------------------------------------------------
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    barrier()
+    with ClockSampler(physical_gpu_index(local)) as clocks:
+        barrier()
+        sec = time_spmm(torch, ops, t, C_out, workspace, ns.kernel, ns.steps, ns.warmup, flush_buf)
+        barrier()
+    sec_max = D.max_over_ranks(sec, dev)
+    flops_total = 2.0 * nnz * Nd
+    value = flops_total / sec_max / 1e9
+
+    # sanity: a sample of this rank's rows against the CPU oracle (outside every timed region)
+    check = None
+    if rank == 0 and not ns.no_extras:
+        import oracle
+        rows = np.unique(np.concatenate([np.random.default_rng(0).integers(0, my_rows, 512),
+                                         np.argsort(np.diff(shard.row_ptr.cpu().numpy()))[-4:]]))
+        rp_l = shard.row_ptr.cpu().numpy().astype(np.int64)
+        idx = np.concatenate([np.arange(rp_l[r], rp_l[r + 1]) for r in rows])
+        idx_d = torch.from_numpy(idx).to(dev)
+        uniq, inv = torch.unique(t["col_idx"][idx_d].long(), return_inverse=True)
+        sub_rp = np.zeros(len(rows) + 1, np.int32)
+        np.cumsum(rp_l[rows + 1] - rp_l[rows], out=sub_rp[1:])
+        f64, mag = oracle.spmm_f64(sub_rp, inv.to(torch.int32).cpu().numpy(), t["values"][idx_d].cpu().numpy(),
+                                   B[uniq].cpu().numpy(), threads=oracle.max_threads())
+        got = C_out[torch.from_numpy(rows).to(dev)].cpu().numpy()
+        check = bool((np.abs(got - f64) <= 1e-5 * mag + 1e-6).all())
+
+    # ---- end to end: pinned host buffers through csrspmm_b200_spmm_host ------------------------------
+    e2e = None
+    if not ns.no_extras:
+        h = {k: torch.empty(v.shape, dtype=v.dtype, pin_memory=True) for k, v in t.items()}
+        for k in h:
+            h[k].copy_(t[k])
+        C_host = torch.empty((my_rows, Nd), dtype=torch.float32, pin_memory=True)
+        arena = torch.empty(ops.host_arena_bytes(my_rows, Kd, Nd, my_nnz), dtype=torch.uint8, device=dev)
+        torch.cuda.synchronize()
+
+        def e2e_step():
+            ops.spmm_host(h["row_ptr"], h["col_idx"], h["values"], h["B"], C_host, 1.0, 0.0, kernel=ns.kernel,
+                          arena=arena, device=dev)
+
+        e2e_step()  # warm-up
+        barrier()
+        t0 = time.perf_counter()
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ev0.record()
+        for _ in range(ns.e2e_steps):
+            e2e_step()
+        ev1.record()
+        torch.cuda.synchronize()
+        e2e_sec = max(ev0.elapsed_time(ev1) / 1e3, time.perf_counter() - t0) / ns.e2e_steps
+        e2e_sec = D.max_over_ranks(e2e_sec, dev)
+        h2d = my_nnz * 8 + (my_rows + 1) * 4 + Kd * Nd * 4
+        d2h = my_rows * Nd * 4
+        e2e = {"value": flops_total / e2e_sec / 1e9, "unit": "GFLOPS", "h2d_bytes_per_step": int(h2d),
+               "d2h_bytes_per_step": int(d2h), "ms_per_step": e2e_sec * 1e3, "steps": ns.e2e_steps,
+               "api": "csrspmm_b200_spmm_host (pinned host A, B in; host C out)"}
+        del h, C_host, arena
+
+    if world > 1:
+        barrier()
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return 0
+
+    peak, peak_kind = measured_peak()
+    achieved = my_bytes / sec / 1e9
+    gather_bytes = my_nnz * Nd * 4.0
+    line = {
+        "metric": "SpMM GFLOPS", "value": value, "unit": "GFLOPS", "n_gpus": world, "steps": ns.steps,
+        "warmup": ns.warmup, "ms_per_step": sec_max * 1e3, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": prob.name, "M": M, "Kd": Kd, "Nd": Nd, "nnz": nnz, "alpha": 1.0, "beta": 0.0,
+                   "row_lengths": {k: cfg[k] for k in ("kind", "p", "zipf_a", "mean", "cap") if k in cfg},
+                   "kernel": chosen, "partition": f"rows, equal nnz+rows over {world} GPU(s), imbalance {imbalance:.4f}",
+                   "B": "replicated per GPU (NCCL broadcast outside the timed region)" if world > 1 else "resident",
+                   "l2": "L2 flushed between steps (256 MiB write)" if flush else "inputs larger than L2, back to back",
+                   "broadcast_s": round(t_bcast, 3)},
+        "gpu_launches": ns.steps * launches_per_step,
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     "traffic": NCU_TRAFFIC.get((prob.name, chosen)), "peak_kind": f"of {peak_kind}",
+                     "algorithmic_bytes": my_bytes, "b_rows_touched": touched,
+                     "gather_bytes": gather_bytes, "gather_GBps": gather_bytes / sec / 1e9,
+                     "scope": "rank 0's row block, main kernel + fix-up kernel"},
+        "clocks": clocks.summary(),
+    }
+    if check is not None:
+        line["oracle_check"] = check
+    if e2e is not None:
+        line["e2e"] = e2e
+
+    if world == 1 and not ns.no_extras:
+        import oracle
+        rows = sample_rows_for(ns.workload, M)
+        g, n_s, best = cpu_sample(torch, G, oracle, prob, rows, oracle.max_threads())
+        line["cpu_baseline"] = {"value": g, "unit": "GFLOPS", "cores": oracle.max_threads(), "kind": "port",
+                                "sample": f"rows [0, {rows}) of {M} ({n_s} of {nnz} nnz), B complete on the host, "
+                                          f"best of 2, {best:.2f} s"}
+        del prob, t, B, C_out, workspace, shard
+        torch.cuda.empty_cache()
+        line["other_workloads"] = other_workloads(torch, ops, G, ns, dev, peak)
+
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
+
+def other_workloads(torch, ops, G, ns, dev, peak):
+    """Kernel-only numbers for the other BASELINE configs (1 GPU), each next to cuSPARSE."""
+    out = {}
+    for name in ("cfg2_medium", "cfg3_powerlaw", "cfg4_fp4"):
+        if name == ns.workload:
+            continue
+        try:
+            p = G.make(name, device=dev)
+            t = {"row_ptr": p.row_ptr, "col_idx": p.col_idx, "values": p.values, "B": p.B}
+            C_out = torch.empty((p.M, p.Nd), dtype=torch.float32, device=dev)
+            ws = torch.empty(max(ops.workspace_bytes(p.M, p.Kd, p.Nd, p.nnz), 256), dtype=torch.uint8, device=dev)
+            footprint = p.nnz * 8 + p.M * 4 + (p.Kd + p.M) * p.Nd * 4
+            fb = torch.empty(2 * L2_BYTES, dtype=torch.uint8, device=dev) if footprint < 2 * L2_BYTES else None
+            mx = ops.row_stats(p.row_ptr)["max_row_nnz"]
+            nbytes, _ = problem_bytes(G, t, p.M, p.Nd, p.nnz, p.Kd)
+            flops = 2.0 * p.nnz * p.Nd
+            entry = {"nnz": p.nnz, "max_row_nnz": mx, "l2_flushed": fb is not None, "kernels": {}}
+            for k in ("row", "merge", "tma"):
+                sec = time_spmm(torch, ops, t, C_out, ws, k, 20, 3, fb, max_row_nnz=mx)
+                entry["kernels"][k] = {"gflops": flops / sec / 1e9, "us": sec * 1e6,
+                                       "roofline_frac": nbytes / sec / 1e9 / peak}
+            auto = ops.selected_kernel(p.M, p.Kd, p.Nd, p.nnz, max_row_nnz=mx)
+            entry["auto"] = auto
+            cs = cusparse_via_torch(torch, t, p.M, p.Kd, 20, 3, fb)
+            entry["cusparse_torch"] = {"gflops": flops / cs / 1e9, "us": cs * 1e6} if isinstance(cs, float) else cs
+            if name == "cfg4_fp4":
+                packed, scale = ops.e2m1_quantize(p.values)
+                e = (packed.to(dev), scale, p.nnz)
+                nb4, _ = problem_bytes(G, t, p.M, p.Nd, p.nnz, p.Kd, 0.5)
+                for k in ("row", "merge", "tma"):
+                    sec = time_spmm(torch, ops, t, C_out, ws, k, 20, 3, fb, max_row_nnz=mx, e2m1=e)
+                    entry["kernels"][k + "_e2m1"] = {"gflops": flops / sec / 1e9, "us": sec * 1e6,
+                                                     "roofline_frac": nb4 / sec / 1e9 / peak}
+            out[name] = entry
+            del p, t, C_out, ws, fb
+            torch.cuda.empty_cache()
+        except Exception as e:  # secondary numbers must not take the headline down
+            out[name] = f"failed: {type(e).__name__}: {e}"[:300]
+    return out
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,149 @@
+"""ctypes binding of libcsrspmm_b200.so (the C ABI declared in include/csrspmm_b200.h).
+
+The library is mandatory: there is no Python or CPU fallback for any compute entry point.
+Loading fails loudly when the shared object has not been built.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+PKG = Path(__file__).resolve().parent
+LIB_PATH = PKG / "lib" / "libcsrspmm_b200.so"
+
+OK = 0
+ERR_BAD_ARG, ERR_INVALID_CSR, ERR_UNSUPPORTED, ERR_CUDA, ERR_DEVICE_WAIT, ERR_WORKSPACE, ERR_NO_DEVICE = range(1, 8)
+
+ENTRY_NAIVE, ENTRY_NAIVE_SMEM, ENTRY_WARP_PER_ROW, ENTRY_WARP_PER_ROW_FP4, ENTRY_WARP_PER_ROW_SMEM, \
+    ENTRY_WARP_PER_ROW_SMEM_FP4 = range(6)
+KERNEL_AUTO, KERNEL_ROW, KERNEL_MERGE, KERNEL_TMA = range(4)
+KERNEL_NAMES = {KERNEL_AUTO: "auto", KERNEL_ROW: "row", KERNEL_MERGE: "merge", KERNEL_TMA: "tma"}
+KERNEL_IDS = {v: k for k, v in KERNEL_NAMES.items()}
+VALUES_F32, VALUES_E2M1 = 0, 1
+
+CSR_BAD_ROWPTR0, CSR_BAD_ROWPTR_END, CSR_NOT_MONOTONE, CSR_COL_RANGE, CSR_COL_UNSORTED = 1, 2, 4, 8, 16
+
+# every symbol include/csrspmm_b200.h declares
+EXPORTED_SYMBOLS = (
+    "csrspmm_b200_abi_version", "csrspmm_b200_status_string", "csrspmm_b200_last_error",
+    "csrspmm_b200_spmm", "csrspmm_b200_spmm_sync", "csrspmm_b200_spmm_host",
+    "csrspmm_b200_host_arena_bytes", "csrspmm_b200_workspace_bytes", "csrspmm_b200_select_kernel",
+    "csrspmm_b200_validate_csr_host", "csrspmm_b200_validate_csr_device",
+    "csrspmm_b200_row_stats_device", "csrspmm_b200_partition_rows", "csrspmm_b200_e2m1_scale",
+    "csrspmm_b200_e2m1_encode", "csrspmm_b200_e2m1_decode",
+)
+
+
+class Args(C.Structure):
+    """Mirror of ``csrspmm_b200_args``."""
+    _fields_ = [
+        ("struct_size", C.c_uint32),
+        ("M", C.c_int32),
+        ("Kd", C.c_int32),
+        ("Nd", C.c_int32),
+        ("nnz", C.c_int64),
+        ("row_ptr", C.c_void_p),
+        ("col_idx", C.c_void_p),
+        ("values", C.c_void_p),
+        ("value_format", C.c_int32),
+        ("value_scale", C.c_float),
+        ("B", C.c_void_p),
+        ("ldb", C.c_int64),
+        ("C", C.c_void_p),
+        ("ldc", C.c_int64),
+        ("alpha", C.c_float),
+        ("beta", C.c_float),
+        ("entry", C.c_int32),
+        ("kernel", C.c_int32),
+        ("max_row_nnz", C.c_int32),
+        ("reserved0", C.c_int32),
+        ("workspace", C.c_void_p),
+        ("workspace_bytes", C.c_size_t),
+        ("status_word", C.c_void_p),
+    ]
+
+
+class LibraryMissing(RuntimeError):
+    pass
+
+
+class SpmmError(RuntimeError):
+    def __init__(self, status: int, where: str):
+        L = lib()
+        msg = L.csrspmm_b200_status_string(status).decode()
+        detail = L.csrspmm_b200_last_error().decode()
+        super().__init__(f"{where}: {msg} (status {status}): {detail}")
+        self.status = status
+
+
+_lib = None
+
+
+def lib() -> C.CDLL:
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not LIB_PATH.exists():
+        raise LibraryMissing(
+            f"{LIB_PATH} is missing: build it with `python -m csrspmm_b200.build` "
+            "(there is no fallback path)")
+    L = C.CDLL(str(LIB_PATH))
+    L.csrspmm_b200_abi_version.restype = C.c_int
+    L.csrspmm_b200_status_string.argtypes = [C.c_int]
+    L.csrspmm_b200_status_string.restype = C.c_char_p
+    L.csrspmm_b200_last_error.restype = C.c_char_p
+    for name in ("csrspmm_b200_spmm", "csrspmm_b200_spmm_sync"):
+        fn = getattr(L, name)
+        fn.argtypes = [C.POINTER(Args), C.c_void_p]
+        fn.restype = C.c_int
+    L.csrspmm_b200_spmm_host.argtypes = [C.POINTER(Args), C.c_void_p, C.c_size_t, C.c_void_p]
+    L.csrspmm_b200_spmm_host.restype = C.c_int
+    L.csrspmm_b200_host_arena_bytes.argtypes = [C.POINTER(Args)]
+    L.csrspmm_b200_host_arena_bytes.restype = C.c_size_t
+    L.csrspmm_b200_workspace_bytes.argtypes = [C.POINTER(Args)]
+    L.csrspmm_b200_workspace_bytes.restype = C.c_size_t
+    L.csrspmm_b200_select_kernel.argtypes = [C.POINTER(Args)]
+    L.csrspmm_b200_select_kernel.restype = C.c_int
+    L.csrspmm_b200_validate_csr_host.argtypes = [C.c_int32, C.c_int32, C.c_int64, C.c_void_p, C.c_void_p,
+                                                 C.POINTER(C.c_uint32)]
+    L.csrspmm_b200_validate_csr_host.restype = C.c_int
+    L.csrspmm_b200_validate_csr_device.argtypes = [C.c_int32, C.c_int32, C.c_int64, C.c_void_p, C.c_void_p,
+                                                   C.POINTER(C.c_uint32), C.c_void_p]
+    L.csrspmm_b200_validate_csr_device.restype = C.c_int
+    L.csrspmm_b200_row_stats_device.argtypes = [C.c_int32, C.c_void_p, C.POINTER(C.c_int64), C.c_void_p]
+    L.csrspmm_b200_row_stats_device.restype = C.c_int
+    L.csrspmm_b200_partition_rows.argtypes = [C.c_int32, C.c_void_p, C.c_int32, C.c_double, C.c_void_p]
+    L.csrspmm_b200_partition_rows.restype = C.c_int
+    L.csrspmm_b200_e2m1_scale.argtypes = [C.c_int64, C.c_void_p]
+    L.csrspmm_b200_e2m1_scale.restype = C.c_float
+    L.csrspmm_b200_e2m1_encode.argtypes = [C.c_int64, C.c_void_p, C.c_float, C.c_void_p]
+    L.csrspmm_b200_e2m1_encode.restype = C.c_int
+    L.csrspmm_b200_e2m1_decode.argtypes = [C.c_int64, C.c_void_p, C.c_float, C.c_void_p]
+    L.csrspmm_b200_e2m1_decode.restype = C.c_int
+    if L.csrspmm_b200_abi_version() != 1:
+        raise LibraryMissing(f"{LIB_PATH} has ABI version {L.csrspmm_b200_abi_version()}, expected 1")
+    _lib = L
+    return L
+
+
+def make_args(M, Kd, Nd, nnz, row_ptr=0, col_idx=0, values=0, B=0, Cptr=0, *, ldb=None, ldc=None,
+              alpha=1.0, beta=0.0, entry=ENTRY_NAIVE, kernel=KERNEL_AUTO, max_row_nnz=0,
+              value_format=VALUES_F32, value_scale=1.0, workspace=0, workspace_bytes=0,
+              status_word=0) -> Args:
+    a = Args()
+    a.struct_size = C.sizeof(Args)
+    a.M, a.Kd, a.Nd, a.nnz = int(M), int(Kd), int(Nd), int(nnz)
+    a.row_ptr, a.col_idx, a.values = row_ptr or None, col_idx or None, values or None
+    a.value_format, a.value_scale = int(value_format), float(value_scale)
+    a.B, a.ldb = B or None, int(Nd if ldb is None else ldb)
+    a.C, a.ldc = Cptr or None, int(Nd if ldc is None else ldc)
+    a.alpha, a.beta = float(alpha), float(beta)
+    a.entry, a.kernel, a.max_row_nnz = int(entry), int(kernel), int(max_row_nnz)
+    a.workspace, a.workspace_bytes = workspace or None, int(workspace_bytes)
+    a.status_word = status_word or None
+    return a
+
+
+def check(status: int, where: str) -> None:
+    if status != OK:
+        raise SpmmError(status, where)

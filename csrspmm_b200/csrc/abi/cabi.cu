@@ -1,0 +1,423 @@
+// extern "C" entry points of the kernel library (declared in include/csrspmm_b200.h).
+//
+// This file owns every kernel launch.  It stands where the reference's launchers do
+// (src/host/spmm_launcher.cu:11-171), but chooses the geometry from the problem instead of
+// fixing it, reports failures as status codes instead of ignoring them, and takes the stream
+// from the caller instead of always using the legacy default stream.
+#include <cuda_runtime.h>
+
+#include <cstdio>
+#include <cstring>
+
+#include "../kernels/aux_kernels.cuh"
+#include "../kernels/merge_kernel.cuh"
+#include "../kernels/row_kernel.cuh"
+#include "../kernels/tma_kernel.cuh"
+#include "csrspmm_b200.h"
+#include "plan.h"
+
+using namespace csrspmm_b200;
+
+namespace {
+
+#define CUDA_TRY(expr)                                                                      \
+    do {                                                                                    \
+        cudaError_t e__ = (expr);                                                           \
+        if (e__ != cudaSuccess) {                                                           \
+            set_last_error("%s failed: %s (%s:%d)", #expr, cudaGetErrorString(e__), __FILE__, \
+                           __LINE__);                                                       \
+            return CSRSPMM_B200_ERR_CUDA;                                                   \
+        }                                                                                   \
+    } while (0)
+
+template <int VW, int NV>
+constexpr int unroll_for()
+{
+    return VW == 1 ? 8 : (NV == 1 ? 8 : 4);
+}
+
+template <int G, int NV, int VW, int FMT>
+void launch_row(const SpmmParams& p, const Plan& plan, cudaStream_t st)
+{
+    spmm_row_kernel<G, NV, VW, unroll_for<VW, NV>(), FMT>
+        <<<(unsigned)plan.grid, kRowThreads, 0, st>>>(p);
+}
+
+template <int G, int NV, int VW, int TG, int FMT>
+void launch_merge(const SpmmParams& p, const Plan& plan, cudaStream_t st)
+{
+    spmm_merge_kernel<G, NV, VW, TG, unroll_for<VW, NV>(), FMT>
+        <<<(unsigned)plan.grid, kMergeThreads, 0, st>>>(p);
+}
+
+template <int NV, int FMT>
+cudaError_t launch_tma(const SpmmParams& p, const Plan& plan, cudaStream_t st)
+{
+    auto kern = spmm_tma_kernel<NV, 128, 8, FMT>;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)plan.dynamic_smem);
+    if (e != cudaSuccess) return e;
+    const unsigned slot = (unsigned)(plan.dynamic_smem / (8 * 8));
+    kern<<<(unsigned)plan.grid, kMergeThreads, plan.dynamic_smem, st>>>(p, slot);
+    return cudaSuccess;
+}
+
+template <int VW, int FMT>
+void dispatch_row(const SpmmParams& p, const Plan& plan, cudaStream_t st)
+{
+    switch (plan.shape) {
+        case 0: launch_row<8, 1, VW, FMT>(p, plan, st); break;
+        case 1: launch_row<16, 1, VW, FMT>(p, plan, st); break;
+        case 2: launch_row<32, 1, VW, FMT>(p, plan, st); break;
+        case 3: launch_row<32, 2, VW, FMT>(p, plan, st); break;
+        default: launch_row<32, 4, VW, FMT>(p, plan, st); break;
+    }
+}
+
+template <int VW, int FMT>
+void dispatch_merge(const SpmmParams& p, const Plan& plan, cudaStream_t st)
+{
+    switch (plan.shape) {
+        case 0: launch_merge<8, 1, VW, kShapes[0].TG, FMT>(p, plan, st); break;
+        case 1: launch_merge<16, 1, VW, kShapes[1].TG, FMT>(p, plan, st); break;
+        case 2: launch_merge<32, 1, VW, kShapes[2].TG, FMT>(p, plan, st); break;
+        case 3: launch_merge<32, 2, VW, kShapes[3].TG, FMT>(p, plan, st); break;
+        default: launch_merge<32, 4, VW, kShapes[4].TG, FMT>(p, plan, st); break;
+    }
+}
+
+template <int FMT>
+cudaError_t dispatch_tma(const SpmmParams& p, const Plan& plan, cudaStream_t st)
+{
+    switch (plan.NV) {
+        case 1: return launch_tma<1, FMT>(p, plan, st);
+        case 2: return launch_tma<2, FMT>(p, plan, st);
+        default: return launch_tma<4, FMT>(p, plan, st);
+    }
+}
+
+int enqueue(const csrspmm_b200_args* a, cudaStream_t st)
+{
+    int status = check_args(a, true);
+    if (status != CSRSPMM_B200_OK) return status;
+    if (a->M == 0 || a->Nd == 0) return CSRSPMM_B200_OK;
+
+    Plan plan;
+    status = make_plan(a, &plan);
+    if (status != CSRSPMM_B200_OK) return status;
+
+    SpmmParams p;
+    std::memset(&p, 0, sizeof(p));
+    p.M = a->M;
+    p.Kd = a->Kd;
+    p.Nd = a->Nd;
+    p.nnz = (int)a->nnz;
+    p.ncolv = plan.ncolv;
+    p.num_items = plan.num_items;
+    p.row_ptr = a->row_ptr;
+    p.col_idx = a->col_idx;
+    p.values = a->values;
+    p.value_scale = a->value_scale;
+    p.B = a->B;
+    p.ldb = a->ldb;
+    p.C = a->C;
+    p.ldc = a->ldc;
+    p.alpha = a->alpha;
+    p.beta = a->beta;
+    p.status_word = a->status_word;
+
+    const bool split = plan.kernel != CSRSPMM_B200_KERNEL_ROW;
+    void* ws = nullptr;
+    bool ws_owned = false;
+    if (split) {
+        if (a->workspace != nullptr) {
+            if (a->workspace_bytes < plan.workspace_bytes ||
+                (reinterpret_cast<uintptr_t>(a->workspace) & 255u) != 0) {
+                set_last_error("workspace of %zu bytes at %p: need %zu bytes, 256-byte aligned",
+                               a->workspace_bytes, a->workspace, plan.workspace_bytes);
+                return CSRSPMM_B200_ERR_WORKSPACE;
+            }
+            ws = a->workspace;
+        } else {
+            CUDA_TRY(cudaMallocAsync(&ws, plan.workspace_bytes, st));
+            ws_owned = true;
+        }
+        p.carry_row = static_cast<int*>(ws);
+        p.carry_val = reinterpret_cast<float*>(static_cast<char*>(ws) + plan.carry_row_bytes);
+        p.carry_ld = plan.carry_ld;
+    }
+
+    const bool e2m1 = a->value_format == CSRSPMM_B200_VALUES_E2M1;
+    cudaError_t attr_err = cudaSuccess;
+    if (plan.kernel == CSRSPMM_B200_KERNEL_ROW) {
+        if (plan.VW == 4) {
+            if (e2m1) dispatch_row<4, kValuesE2M1>(p, plan, st);
+            else dispatch_row<4, kValuesF32>(p, plan, st);
+        } else {
+            if (e2m1) dispatch_row<1, kValuesE2M1>(p, plan, st);
+            else dispatch_row<1, kValuesF32>(p, plan, st);
+        }
+    } else if (plan.kernel == CSRSPMM_B200_KERNEL_MERGE) {
+        if (plan.VW == 4) {
+            if (e2m1) dispatch_merge<4, kValuesE2M1>(p, plan, st);
+            else dispatch_merge<4, kValuesF32>(p, plan, st);
+        } else {
+            if (e2m1) dispatch_merge<1, kValuesE2M1>(p, plan, st);
+            else dispatch_merge<1, kValuesF32>(p, plan, st);
+        }
+    } else {
+        attr_err = e2m1 ? dispatch_tma<kValuesE2M1>(p, plan, st) : dispatch_tma<kValuesF32>(p, plan, st);
+    }
+    cudaError_t err = attr_err != cudaSuccess ? attr_err : cudaGetLastError();
+
+    if (err == cudaSuccess && split) {
+        const int warps = 256 / 32;
+        const unsigned grid = (unsigned)((plan.num_tiles + warps - 1) / warps);
+        if (plan.VW == 4) spmm_fixup_kernel<4><<<grid, 256, 0, st>>>(p, (int)plan.num_tiles);
+        else spmm_fixup_kernel<1><<<grid, 256, 0, st>>>(p, (int)plan.num_tiles);
+        err = cudaGetLastError();
+    }
+    if (ws_owned) {
+        cudaError_t ferr = cudaFreeAsync(ws, st);
+        if (err == cudaSuccess) err = ferr;
+    }
+    if (err != cudaSuccess) {
+        set_last_error("kernel launch failed: %s", cudaGetErrorString(err));
+        return CSRSPMM_B200_ERR_CUDA;
+    }
+    return CSRSPMM_B200_OK;
+}
+
+size_t align256(size_t v) { return (v + 255) / 256 * 256; }
+
+}  // namespace
+
+extern "C" {
+
+int csrspmm_b200_abi_version(void) { return CSRSPMM_B200_ABI_VERSION; }
+
+const char* csrspmm_b200_status_string(int status)
+{
+    switch (status) {
+        case CSRSPMM_B200_OK: return "ok";
+        case CSRSPMM_B200_ERR_BAD_ARG: return "bad argument";
+        case CSRSPMM_B200_ERR_INVALID_CSR: return "invalid CSR matrix";
+        case CSRSPMM_B200_ERR_UNSUPPORTED: return "unsupported shape or layout for the requested kernel";
+        case CSRSPMM_B200_ERR_CUDA: return "CUDA error";
+        case CSRSPMM_B200_ERR_DEVICE_WAIT: return "device-side wait gave up";
+        case CSRSPMM_B200_ERR_WORKSPACE: return "workspace too small or misaligned";
+        case CSRSPMM_B200_ERR_NO_DEVICE: return "no usable device";
+        default: return "unknown status";
+    }
+}
+
+const char* csrspmm_b200_last_error(void) { return get_last_error(); }
+
+int csrspmm_b200_spmm(const csrspmm_b200_args* args, csrspmm_b200_stream_t stream)
+{
+    return enqueue(args, reinterpret_cast<cudaStream_t>(stream));
+}
+
+int csrspmm_b200_spmm_sync(const csrspmm_b200_args* args, csrspmm_b200_stream_t stream)
+{
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    int status = enqueue(args, st);
+    if (status != CSRSPMM_B200_OK) return status;
+    CUDA_TRY(cudaStreamSynchronize(st));
+    if (args->status_word != nullptr) {
+        int word = 0;
+        CUDA_TRY(cudaMemcpy(&word, args->status_word, sizeof(int), cudaMemcpyDeviceToHost));
+        if (word & kStatusWaitTimeout) {
+            set_last_error("device status word 0x%x: a bounded wait gave up", word);
+            return CSRSPMM_B200_ERR_DEVICE_WAIT;
+        }
+        if (word & (kStatusBadTile | kStatusColClamped)) {
+            set_last_error("device status word 0x%x: malformed CSR (row_ptr or col_idx)", word);
+            return CSRSPMM_B200_ERR_INVALID_CSR;
+        }
+    }
+    return CSRSPMM_B200_OK;
+}
+
+size_t csrspmm_b200_workspace_bytes(const csrspmm_b200_args* args) { return worst_case_workspace(args); }
+
+int csrspmm_b200_select_kernel(const csrspmm_b200_args* args)
+{
+    Plan plan;
+    int status = make_plan(args, &plan);
+    if (status != CSRSPMM_B200_OK) return -status;
+    return plan.kernel;
+}
+
+size_t csrspmm_b200_host_arena_bytes(const csrspmm_b200_args* a)
+{
+    if (check_args(a, false) != CSRSPMM_B200_OK) return 0;
+    const size_t vbytes = a->value_format == CSRSPMM_B200_VALUES_E2M1 ? (size_t)(a->nnz + 1) / 2
+                                                                      : (size_t)a->nnz * 4;
+    size_t total = 0;
+    total += align256(((size_t)a->M + 1) * 4);
+    total += align256((size_t)a->nnz * 4);
+    total += align256(vbytes);
+    total += align256((size_t)a->Kd * (size_t)a->Nd * 4);
+    total += align256((size_t)a->M * (size_t)a->Nd * 4);
+    total += align256(worst_case_workspace(a));
+    total += 256;  // status word
+    return total;
+}
+
+int csrspmm_b200_spmm_host(const csrspmm_b200_args* a, void* device_arena, size_t device_arena_bytes,
+                           csrspmm_b200_stream_t stream)
+{
+    int status = check_args(a, true);
+    if (status != CSRSPMM_B200_OK) return status;
+    if (a->M == 0 || a->Nd == 0) return CSRSPMM_B200_OK;
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    const size_t need = csrspmm_b200_host_arena_bytes(a);
+    char* arena = static_cast<char*>(device_arena);
+    bool owned = false;
+    if (arena == nullptr) {
+        CUDA_TRY(cudaMallocAsync(reinterpret_cast<void**>(&arena), need, st));
+        owned = true;
+    } else if (device_arena_bytes < need || (reinterpret_cast<uintptr_t>(arena) & 255u) != 0) {
+        set_last_error("device arena of %zu bytes: need %zu bytes, 256-byte aligned",
+                       device_arena_bytes, need);
+        return CSRSPMM_B200_ERR_WORKSPACE;
+    }
+
+    const size_t vbytes = a->value_format == CSRSPMM_B200_VALUES_E2M1 ? (size_t)(a->nnz + 1) / 2
+                                                                      : (size_t)a->nnz * 4;
+    const size_t rp_bytes = ((size_t)a->M + 1) * 4, ci_bytes = (size_t)a->nnz * 4;
+    const size_t c_bytes = (size_t)a->M * (size_t)a->Nd * 4;
+    const size_t ws_bytes = worst_case_workspace(a);
+    char* cur = arena;
+    int32_t* d_rp = reinterpret_cast<int32_t*>(cur); cur += align256(rp_bytes);
+    int32_t* d_ci = reinterpret_cast<int32_t*>(cur); cur += align256(ci_bytes);
+    void* d_va = cur; cur += align256(vbytes);
+    float* d_B = reinterpret_cast<float*>(cur); cur += align256((size_t)a->Kd * (size_t)a->Nd * 4);
+    float* d_C = reinterpret_cast<float*>(cur); cur += align256(c_bytes);
+    void* d_ws = cur; cur += align256(ws_bytes);
+    int32_t* d_status = reinterpret_cast<int32_t*>(cur);
+
+    auto fail = [&](int code) {
+        if (owned) cudaFreeAsync(arena, st);
+        return code;
+    };
+#define CUDA_TRY_HOST(expr)                                                                 \
+    do {                                                                                    \
+        cudaError_t e__ = (expr);                                                           \
+        if (e__ != cudaSuccess) {                                                           \
+            set_last_error("%s failed: %s", #expr, cudaGetErrorString(e__));                \
+            return fail(CSRSPMM_B200_ERR_CUDA);                                             \
+        }                                                                                   \
+    } while (0)
+
+    CUDA_TRY_HOST(cudaMemsetAsync(d_status, 0, 4, st));
+    CUDA_TRY_HOST(cudaMemcpyAsync(d_rp, a->row_ptr, rp_bytes, cudaMemcpyHostToDevice, st));
+    if (a->nnz > 0) {
+        CUDA_TRY_HOST(cudaMemcpyAsync(d_ci, a->col_idx, ci_bytes, cudaMemcpyHostToDevice, st));
+        CUDA_TRY_HOST(cudaMemcpyAsync(d_va, a->values, vbytes, cudaMemcpyHostToDevice, st));
+    }
+    if (a->Kd > 0) {
+        // B rows are packed on the device (ldb = Nd) whatever the host stride is
+        CUDA_TRY_HOST(cudaMemcpy2DAsync(d_B, (size_t)a->Nd * 4, a->B, (size_t)a->ldb * 4,
+                                        (size_t)a->Nd * 4, (size_t)a->Kd, cudaMemcpyHostToDevice, st));
+    }
+    if (a->beta != 0.0f) {
+        CUDA_TRY_HOST(cudaMemcpy2DAsync(d_C, (size_t)a->Nd * 4, a->C, (size_t)a->ldc * 4,
+                                        (size_t)a->Nd * 4, (size_t)a->M, cudaMemcpyHostToDevice, st));
+    }
+    csrspmm_b200_args d = *a;
+    d.row_ptr = d_rp;
+    d.col_idx = d_ci;
+    d.values = d_va;
+    d.B = d_B;
+    d.ldb = a->Nd;
+    d.C = d_C;
+    d.ldc = a->Nd;
+    d.workspace = d_ws;
+    d.workspace_bytes = align256(ws_bytes);
+    d.status_word = d_status;
+    status = enqueue(&d, st);
+    if (status != CSRSPMM_B200_OK) return fail(status);
+    CUDA_TRY_HOST(cudaMemcpy2DAsync(a->C, (size_t)a->ldc * 4, d_C, (size_t)a->Nd * 4, (size_t)a->Nd * 4,
+                                    (size_t)a->M, cudaMemcpyDeviceToHost, st));
+    int word = 0;
+    CUDA_TRY_HOST(cudaMemcpyAsync(&word, d_status, 4, cudaMemcpyDeviceToHost, st));
+    if (owned) CUDA_TRY_HOST(cudaFreeAsync(arena, st));
+    owned = false;
+    CUDA_TRY_HOST(cudaStreamSynchronize(st));
+    if (word & kStatusWaitTimeout) {
+        set_last_error("device status word 0x%x: a bounded wait gave up", word);
+        return CSRSPMM_B200_ERR_DEVICE_WAIT;
+    }
+    if (word != 0) {
+        set_last_error("device status word 0x%x: malformed CSR (row_ptr or col_idx)", word);
+        return CSRSPMM_B200_ERR_INVALID_CSR;
+    }
+    return CSRSPMM_B200_OK;
+#undef CUDA_TRY_HOST
+}
+
+int csrspmm_b200_validate_csr_device(int32_t M, int32_t Kd, int64_t nnz, const int32_t* row_ptr,
+                                     const int32_t* col_idx, uint32_t* problems,
+                                     csrspmm_b200_stream_t stream)
+{
+    if (M < 0 || Kd < 0 || nnz < 0 || row_ptr == nullptr || (nnz > 0 && col_idx == nullptr) ||
+        problems == nullptr) {
+        set_last_error("validate_csr_device: bad argument");
+        return CSRSPMM_B200_ERR_BAD_ARG;
+    }
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    unsigned* d_flags = nullptr;
+    CUDA_TRY(cudaMallocAsync(reinterpret_cast<void**>(&d_flags), sizeof(unsigned), st));
+    CUDA_TRY(cudaMemsetAsync(d_flags, 0, sizeof(unsigned), st));
+    const int threads = 256;
+    long long blocks = ((long long)M + threads - 1) / threads;
+    if (blocks < 1) blocks = 1;
+    if (blocks > 148 * 32) blocks = 148 * 32;
+    validate_csr_kernel<<<(unsigned)blocks, threads, 0, st>>>(M, Kd, nnz, row_ptr, col_idx, d_flags);
+    CUDA_TRY(cudaGetLastError());
+    unsigned flags = 0;
+    CUDA_TRY(cudaMemcpyAsync(&flags, d_flags, sizeof(unsigned), cudaMemcpyDeviceToHost, st));
+    CUDA_TRY(cudaFreeAsync(d_flags, st));
+    CUDA_TRY(cudaStreamSynchronize(st));
+    *problems = flags;
+    if (flags & 15u) {
+        set_last_error("CSR validation failed, problem bits 0x%x", flags);
+        return CSRSPMM_B200_ERR_INVALID_CSR;
+    }
+    return CSRSPMM_B200_OK;
+}
+
+int csrspmm_b200_row_stats_device(int32_t M, const int32_t* row_ptr, int64_t stats[4],
+                                  csrspmm_b200_stream_t stream)
+{
+    if (M < 0 || row_ptr == nullptr || stats == nullptr) {
+        set_last_error("row_stats_device: bad argument");
+        return CSRSPMM_B200_ERR_BAD_ARG;
+    }
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    int first = 0, last = 0;
+    CUDA_TRY(cudaMemcpyAsync(&first, row_ptr, 4, cudaMemcpyDeviceToHost, st));
+    CUDA_TRY(cudaMemcpyAsync(&last, row_ptr + M, 4, cudaMemcpyDeviceToHost, st));
+    CUDA_TRY(cudaStreamSynchronize(st));
+    const long long nnz = (long long)last - first;
+    const long long mean = M > 0 ? nnz / M : 0;
+    unsigned long long* d_stats = nullptr;
+    CUDA_TRY(cudaMallocAsync(reinterpret_cast<void**>(&d_stats), 4 * sizeof(unsigned long long), st));
+    CUDA_TRY(cudaMemsetAsync(d_stats, 0, 4 * sizeof(unsigned long long), st));
+    const int threads = 256;
+    long long blocks = ((long long)M + threads - 1) / threads;
+    if (blocks < 1) blocks = 1;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    row_stats_kernel<<<(unsigned)blocks, threads, 0, st>>>(M, row_ptr, 32 * (mean + 1), d_stats);
+    CUDA_TRY(cudaGetLastError());
+    unsigned long long h[4] = {0, 0, 0, 0};
+    CUDA_TRY(cudaMemcpyAsync(h, d_stats, sizeof(h), cudaMemcpyDeviceToHost, st));
+    CUDA_TRY(cudaFreeAsync(d_stats, st));
+    CUDA_TRY(cudaStreamSynchronize(st));
+    for (int k = 0; k < 4; ++k) stats[k] = (int64_t)h[k];
+    return CSRSPMM_B200_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,189 @@
+// Host-only launch planning (see plan.h).
+#include "plan.h"
+
+#include <cstdarg>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+
+namespace csrspmm_b200 {
+
+namespace {
+thread_local char g_last_error[512] = "";
+
+inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+}  // namespace
+
+void set_last_error(const char* fmt, ...)
+{
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_last_error, sizeof(g_last_error), fmt, ap);
+    va_end(ap);
+}
+
+const char* get_last_error() { return g_last_error; }
+
+int check_args(const csrspmm_b200_args* a, bool need_pointers)
+{
+    if (a == nullptr) {
+        set_last_error("args is null");
+        return CSRSPMM_B200_ERR_BAD_ARG;
+    }
+    if (a->struct_size != sizeof(csrspmm_b200_args)) {
+        set_last_error("args.struct_size is %u, this library expects %zu", a->struct_size,
+                       sizeof(csrspmm_b200_args));
+        return CSRSPMM_B200_ERR_BAD_ARG;
+    }
+    if (a->M < 0 || a->Kd < 0 || a->Nd < 0 || a->nnz < 0 || a->nnz > 0x7fffffffLL) {
+        set_last_error("negative or oversized dimension (M=%d Kd=%d Nd=%d nnz=%lld)", a->M, a->Kd,
+                       a->Nd, (long long)a->nnz);
+        return CSRSPMM_B200_ERR_BAD_ARG;
+    }
+    if (a->nnz > 0 && a->Kd == 0) {
+        set_last_error("nnz > 0 with Kd == 0");
+        return CSRSPMM_B200_ERR_BAD_ARG;
+    }
+    if (a->ldb < a->Nd || a->ldc < a->Nd) {
+        set_last_error("leading dimension smaller than Nd (ldb=%lld ldc=%lld Nd=%d)",
+                       (long long)a->ldb, (long long)a->ldc, a->Nd);
+        return CSRSPMM_B200_ERR_BAD_ARG;
+    }
+    if (a->value_format != CSRSPMM_B200_VALUES_F32 && a->value_format != CSRSPMM_B200_VALUES_E2M1) {
+        set_last_error("unknown value_format %d", a->value_format);
+        return CSRSPMM_B200_ERR_BAD_ARG;
+    }
+    if (a->entry < CSRSPMM_B200_ENTRY_NAIVE || a->entry > CSRSPMM_B200_ENTRY_WARP_PER_ROW_SMEM_FP4) {
+        set_last_error("unknown entry %d", a->entry);
+        return CSRSPMM_B200_ERR_BAD_ARG;
+    }
+    if (a->kernel < CSRSPMM_B200_KERNEL_AUTO || a->kernel > CSRSPMM_B200_KERNEL_TMA) {
+        set_last_error("unknown kernel %d", a->kernel);
+        return CSRSPMM_B200_ERR_BAD_ARG;
+    }
+    if (need_pointers && a->M > 0 && a->Nd > 0) {
+        if (a->row_ptr == nullptr || a->C == nullptr ||
+            (a->nnz > 0 && (a->col_idx == nullptr || a->values == nullptr || a->B == nullptr))) {
+            set_last_error("null matrix pointer");
+            return CSRSPMM_B200_ERR_BAD_ARG;
+        }
+    }
+    return CSRSPMM_B200_OK;
+}
+
+bool vector_layout_ok(const csrspmm_b200_args* a)
+{
+    return a->Nd % 4 == 0 && a->ldb % 4 == 0 && a->ldc % 4 == 0 &&
+           (reinterpret_cast<uintptr_t>(a->B) & 15u) == 0 &&
+           (reinterpret_cast<uintptr_t>(a->C) & 15u) == 0;
+}
+
+static int shape_for(int ncolv)
+{
+    if (ncolv <= 8) return 0;
+    if (ncolv <= 16) return 1;
+    if (ncolv <= 32) return 2;
+    if (ncolv <= 64) return 3;
+    return 4;
+}
+
+static bool tma_can_run(const csrspmm_b200_args* a)
+{
+    return vector_layout_ok(a) && a->Nd >= 4 && a->Nd <= 512;
+}
+
+static int forced_kernel_from_env()
+{
+    const char* e = std::getenv("CSRSPMM_FORCE_KERNEL");
+    if (e == nullptr || *e == 0) return CSRSPMM_B200_KERNEL_AUTO;
+    if (!std::strcmp(e, "row")) return CSRSPMM_B200_KERNEL_ROW;
+    if (!std::strcmp(e, "merge")) return CSRSPMM_B200_KERNEL_MERGE;
+    if (!std::strcmp(e, "tma")) return CSRSPMM_B200_KERNEL_TMA;
+    return CSRSPMM_B200_KERNEL_AUTO;
+}
+
+static void fill_split_geometry(const csrspmm_b200_args* a, Plan* plan, int tile)
+{
+    plan->tile = tile;
+    plan->num_items = (long long)a->M + a->nnz;
+    plan->num_tiles = (plan->num_items + tile - 1) / tile;
+    plan->grid = plan->num_tiles;
+    plan->carry_ld = ((long long)a->Nd + 3) / 4 * 4;
+    plan->carry_row_bytes = align_up((size_t)plan->num_tiles * sizeof(int32_t), 256);
+    plan->workspace_bytes =
+        plan->carry_row_bytes + (size_t)plan->num_tiles * (size_t)plan->carry_ld * sizeof(float);
+}
+
+int make_plan(const csrspmm_b200_args* a, Plan* plan)
+{
+    int st = check_args(a, false);
+    if (st != CSRSPMM_B200_OK) return st;
+    *plan = Plan();
+    const bool vec = vector_layout_ok(a);
+    plan->VW = vec ? 4 : 1;
+    plan->ncolv = vec ? a->Nd / 4 : a->Nd;
+    plan->num_items = (long long)a->M + a->nnz;
+
+    int kernel = a->kernel;
+    bool forced = kernel != CSRSPMM_B200_KERNEL_AUTO;
+    if (!forced) {
+        kernel = forced_kernel_from_env();
+        // an environment override that cannot run this layout falls back to AUTO
+        if (kernel == CSRSPMM_B200_KERNEL_TMA && !tma_can_run(a)) kernel = CSRSPMM_B200_KERNEL_AUTO;
+    }
+    if (kernel == CSRSPMM_B200_KERNEL_AUTO) {
+        const double avg = a->M > 0 ? (double)a->nnz / (double)a->M : 0.0;
+        const bool smem_entry = a->entry == CSRSPMM_B200_ENTRY_WARP_PER_ROW_SMEM ||
+                                a->entry == CSRSPMM_B200_ENTRY_WARP_PER_ROW_SMEM_FP4 ||
+                                a->entry == CSRSPMM_B200_ENTRY_NAIVE_SMEM;
+        const double row_limit = avg * 4.0 > 64.0 ? avg * 4.0 : 64.0;
+        if (smem_entry && tma_can_run(a) && a->Nd >= 64)
+            kernel = CSRSPMM_B200_KERNEL_TMA;
+        else if (a->max_row_nnz > 0 && (double)a->max_row_nnz <= row_limit)
+            kernel = CSRSPMM_B200_KERNEL_ROW;
+        else
+            kernel = CSRSPMM_B200_KERNEL_MERGE;
+    }
+    if (kernel == CSRSPMM_B200_KERNEL_TMA && !tma_can_run(a)) {
+        set_last_error("the TMA kernel needs Nd %% 4 == 0, Nd <= 512, ldb/ldc %% 4 == 0 and "
+                       "16-byte aligned B and C (Nd=%d ldb=%lld ldc=%lld)",
+                       a->Nd, (long long)a->ldb, (long long)a->ldc);
+        return CSRSPMM_B200_ERR_UNSUPPORTED;
+    }
+    plan->kernel = kernel;
+
+    if (kernel == CSRSPMM_B200_KERNEL_TMA) {
+        plan->G = 32;
+        plan->NV = plan->ncolv <= 32 ? 1 : (plan->ncolv <= 64 ? 2 : 4);
+        plan->shape = plan->NV == 1 ? 2 : (plan->NV == 2 ? 3 : 4);
+        fill_split_geometry(a, plan, 8 * 128);
+        const size_t slot = align_up((size_t)a->Nd * 4, 128);
+        plan->dynamic_smem = 8 /*warps*/ * 8 /*slots*/ * slot;
+    } else {
+        plan->shape = shape_for(plan->ncolv);
+        plan->G = kShapes[plan->shape].G;
+        plan->NV = kShapes[plan->shape].NV;
+        if (kernel == CSRSPMM_B200_KERNEL_MERGE) {
+            fill_split_geometry(a, plan, (256 / plan->G) * kShapes[plan->shape].TG);
+        } else {
+            const int groups = 256 / plan->G;
+            plan->grid = ((long long)a->M + groups - 1) / groups;
+        }
+    }
+    if (plan->grid > 0x7fffffffLL) {
+        set_last_error("grid of %lld CTAs exceeds the launch limit", plan->grid);
+        return CSRSPMM_B200_ERR_UNSUPPORTED;
+    }
+    return CSRSPMM_B200_OK;
+}
+
+size_t worst_case_workspace(const csrspmm_b200_args* a)
+{
+    if (check_args(a, false) != CSRSPMM_B200_OK) return 0;
+    // the smallest tile any split kernel uses is 1024 items
+    Plan p;
+    fill_split_geometry(a, &p, 1024);
+    return p.workspace_bytes;
+}
+
+}  // namespace csrspmm_b200

@@ -1,0 +1,54 @@
+// Host-only launch planning for the SpMM entry point: which kernel, which lane-group shape,
+// how many tiles, how much scratch.  Pure C++ (no CUDA call), so it can be unit-tested on a
+// machine without a GPU.  Replaces the fixed geometry of the reference's launchers
+// (src/host/spmm_launcher.cu:17-19, 63-66, 112-120) and the stub auto-selection of
+// src/csrspmm.cpp:34-40.
+#pragma once
+
+#include <cstddef>
+#include <cstdint>
+
+#include "csrspmm_b200.h"
+
+namespace csrspmm_b200 {
+
+struct Plan {
+    int kernel = CSRSPMM_B200_KERNEL_ROW;  // resolved, never AUTO
+    int shape = 0;                         // index into kShapes
+    int G = 8, NV = 1, VW = 4;             // lanes per group, vectors per lane, vector width
+    int ncolv = 0;                         // ceil(Nd / VW)
+    int tile = 0;                          // merge-path items per CTA (split kernels)
+    long long num_items = 0;               // M + nnz
+    long long num_tiles = 0;               // CTAs of the split kernels
+    long long grid = 0;                    // CTAs of the main kernel
+    long long carry_ld = 0;                // floats per carry row
+    size_t carry_row_bytes = 0;            // 256-byte aligned
+    size_t workspace_bytes = 0;            // carry_row_bytes + carry values
+    size_t dynamic_smem = 0;               // TMA kernel only
+};
+
+struct ShapeDesc {
+    int G, NV, TG;  // TG = merge-path items per lane group
+};
+constexpr int kNumShapes = 5;
+constexpr ShapeDesc kShapes[kNumShapes] = {
+    {8, 1, 64}, {16, 1, 128}, {32, 1, 128}, {32, 2, 128}, {32, 4, 128}};
+
+// Checks the argument block (sizes, enums, pointers) without touching memory.
+int check_args(const csrspmm_b200_args* a, bool need_pointers);
+
+// True when every row of B and C, and both base pointers, allow 16-byte vector access.
+bool vector_layout_ok(const csrspmm_b200_args* a);
+
+// Resolves AUTO (and the CSRSPMM_FORCE_KERNEL override) and fills the launch geometry.
+// Returns CSRSPMM_B200_OK or an error status.
+int make_plan(const csrspmm_b200_args* a, Plan* plan);
+
+// Workspace of the split kernels for a given plan-independent worst case: what
+// csrspmm_b200_workspace_bytes reports (the larger of the MERGE and TMA needs).
+size_t worst_case_workspace(const csrspmm_b200_args* a);
+
+void set_last_error(const char* fmt, ...);
+const char* get_last_error();
+
+}  // namespace csrspmm_b200

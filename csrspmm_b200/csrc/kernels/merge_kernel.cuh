@@ -1,0 +1,320 @@
+// Merge-path kernel: equal shares of (rows + non-zeros) per CTA and per lane group.
+//
+// Serves every entry point of the reference on matrices whose rows are long or uneven, where a
+// whole-row mapping (src/device/csrspmm_warp_per_row.cu:24-43: one warp walks one row from start
+// to end) leaves most of the chip waiting for the longest row.
+//
+// The list of row ends (row_ptr[1..M]) is merged with the list of non-zero positions
+// (0..nnz-1); consuming a row end means "row finished, write it", consuming a position means
+// "one multiply-add per output column".  Diagonal d of that merge is found by binary search,
+// so CTA t owns items [t*TILE, (t+1)*TILE) and lane group g of the CTA owns TG of them, whatever
+// the row lengths are.
+//
+//   1. two warps search the CTA's two diagonals in row_ptr (32 probes per step);
+//   2. the CTA copies its slice of row ends, column indices and (decoded) values to shared
+//      memory with coalesced loads;
+//   3. each group finds its own sub-range in shared memory and walks it: U B-row loads in
+//      flight per lane, FMAs in stored order, a row written when its end is passed;
+//   4. a row that several groups of the CTA worked on is summed through shared memory (the
+//      group that passes its end holds the write back until the others have published their
+//      partial sums), so rows inside one CTA never touch global scratch;
+//   5. the one row a CTA leaves unfinished goes to carry_row/carry_val[blockIdx.x]; the fix-up
+//      kernel adds those to C in tile order.  No atomics: the result is the same on every run.
+//
+// A row that lies inside one group's range is accumulated sequentially and matches the oracle
+// bit for bit; a split row is a fixed-order sum of sequential partial sums.
+#pragma once
+
+#include <limits.h>
+
+#include "common.cuh"
+
+namespace csrspmm_b200 {
+
+constexpr int kMergeThreads = 256;
+
+// First i in [max(0, d-nnz), min(d, M)] with row_end[i] > d - i - 1; then j = d - i positions
+// precede the diagonal.  Cooperative over one full warp: 32 probes per round.
+__device__ __forceinline__ int merge_search_warp(long long d, const int* __restrict__ row_end,
+                                                 int M, int nnz, int lane)
+{
+    int lo = (int)max(0LL, d - (long long)nnz);
+    int hi = (int)min(d, (long long)M);
+    while (lo < hi) {
+        const int span = hi - lo;
+        const int step = (span + 31) / 32;
+        const long long mid = (long long)lo + (long long)lane * step;
+        bool pred = false;
+        if (mid < hi) pred = ((long long)__ldg(row_end + mid) <= d - mid - 1);
+        const int t = __popc(__ballot_sync(0xffffffffu, pred));
+        if (t == 0) {
+            hi = lo;
+        } else {
+            const long long first_false = (long long)lo + (long long)t * step;
+            lo = lo + (t - 1) * step + 1;
+            hi = (int)min((long long)hi, first_false);
+            if (hi < lo) hi = lo;  // only reachable when row_ptr is not monotone
+        }
+    }
+    return lo;
+}
+
+// Same search inside the CTA's shared-memory slice (local coordinates).
+__device__ __forceinline__ int merge_search_local(int d, const int* s_rowend, int nrows, int nnzt)
+{
+    int lo = max(0, d - nnzt);
+    int hi = min(d, nrows);
+    while (lo < hi) {
+        const int mid = (lo + hi) >> 1;
+        if (s_rowend[mid] <= d - mid - 1) lo = mid + 1;
+        else hi = mid;
+    }
+    return lo;
+}
+
+template <int G, int NV, int VW, int TG>
+struct MergeSmem {
+    static constexpr int GROUPS = kMergeThreads / G;
+    static constexpr int TILE = GROUPS * TG;
+    static constexpr int ROWW = G * NV * VW;  // floats one group holds per pass
+    int rowend[TILE + 1];
+    int col[TILE];
+    float val[TILE];
+    int coord[4];
+    int tail_row[GROUPS];
+    alignas(16) float tail[GROUPS][ROWW];
+};
+
+// Where a lane group's share of the tile starts and ends, in tile-local coordinates.
+struct TileRange {
+    int i0, j0;      // global row / non-zero position where the tile starts
+    int nrows;       // row ends inside the tile
+    int nnzt;        // non-zeros inside the tile
+    int il0, jl0;    // the group's start (local row, local non-zero)
+    int il1, jl1;    // the group's end
+};
+
+// Steps 1-3.  Returns false (for every thread of the CTA) when row_ptr is inconsistent.
+template <class Smem, int G, int TG, int FMT>
+__device__ __forceinline__ bool merge_tile_setup(const SpmmParams& p, Smem& s, TileRange& r)
+{
+    constexpr int TILE = Smem::TILE;
+    const int tid = threadIdx.x;
+    const int warp = tid >> 5;
+    const int* __restrict__ row_end = p.row_ptr + 1;
+
+    // ---- 1. the CTA's two diagonals --------------------------------------------------------
+    const long long d0 = (long long)blockIdx.x * TILE;
+    const long long d1 = min(d0 + (long long)TILE, p.num_items);
+    if (warp < 2) {
+        const long long d = warp == 0 ? d0 : d1;
+        const int i = merge_search_warp(d, row_end, p.M, p.nnz, tid & 31);
+        if ((tid & 31) == 0) {
+            s.coord[warp * 2] = i;
+            s.coord[warp * 2 + 1] = (int)(d - i);
+        }
+    }
+    __syncthreads();
+    r.i0 = s.coord[0];
+    r.j0 = s.coord[1];
+    r.nrows = s.coord[2] - r.i0;
+    r.nnzt = s.coord[3] - r.j0;
+    if (r.nrows < 0 || r.nnzt < 0 || r.nrows + r.nnzt > TILE) {  // malformed row_ptr: touch nothing
+        if (tid == 0) {
+            report_status(p, kStatusBadTile);
+            p.carry_row[blockIdx.x] = -1;
+        }
+        return false;
+    }
+
+    // ---- 2. stage the slice ----------------------------------------------------------------
+    for (int k = tid; k <= r.nrows; k += kMergeThreads)
+        s.rowend[k] = (k < r.nrows) ? (__ldg(row_end + r.i0 + k) - r.j0) : INT_MAX;
+    for (int k = tid; k < r.nnzt; k += kMergeThreads) {
+        int c = __ldcs(p.col_idx + r.j0 + k);
+        if ((unsigned)c >= (unsigned)p.Kd) {  // never fault on a bad index
+            c = min(max(c, 0), p.Kd - 1);
+            report_status(p, kStatusColClamped);
+        }
+        s.col[k] = c;
+        s.val[k] = load_value<FMT>(p.values, r.j0 + k, p.value_scale);
+    }
+    __syncthreads();
+
+    // ---- 3. the group's own range ----------------------------------------------------------
+    const int g = tid / G;
+    const int total = r.nrows + r.nnzt;
+    const int dl0 = min(g * TG, total);
+    const int dl1 = min(dl0 + TG, total);
+    r.il0 = merge_search_local(dl0, s.rowend, r.nrows, r.nnzt);
+    r.jl0 = dl0 - r.il0;
+    r.il1 = merge_search_local(dl1, s.rowend, r.nrows, r.nnzt);
+    r.jl1 = dl1 - r.il1;
+    return true;
+}
+
+// Steps 4-5 for one column pass.  acc = the group's unfinished partial sum (valid when dirty),
+// head = its held-back first finished row (valid when il1 > il0).  Contains one __syncthreads.
+template <class Smem, int G, int NV, int VW>
+__device__ __forceinline__ void merge_tile_finish(const SpmmParams& p, Smem& s, const TileRange& r,
+                                                  int cb, int g, int lane, const Vec<VW> (&acc)[NV],
+                                                  Vec<VW> (&head)[NV], bool dirty)
+{
+    constexpr int GROUPS = Smem::GROUPS;
+    // ---- 4. rows shared between groups of this CTA -------------------------------------------
+    if (lane == 0) s.tail_row[g] = dirty ? r.il1 : -1;
+    if (dirty) {
+#pragma unroll
+        for (int v = 0; v < NV; ++v) acc[v].store(&s.tail[g][(lane + v * G) * VW]);
+    }
+    __syncthreads();
+
+    if (r.il1 > r.il0) {
+        // earlier groups' partial sums of my first row, oldest first, then my own part
+        int gs = g;
+        while (gs > 0 && s.tail_row[gs - 1] == r.il0) --gs;
+        if (gs < g) {
+            Vec<VW> sum[NV];
+#pragma unroll
+            for (int v = 0; v < NV; ++v) sum[v].load(&s.tail[gs][(lane + v * G) * VW]);
+            for (int q = gs + 1; q < g; ++q) {
+#pragma unroll
+                for (int v = 0; v < NV; ++v) {
+                    Vec<VW> t;
+                    t.load(&s.tail[q][(lane + v * G) * VW]);
+                    sum[v].add(t);
+                }
+            }
+#pragma unroll
+            for (int v = 0; v < NV; ++v) {
+                sum[v].add(head[v]);
+                head[v] = sum[v];
+            }
+        }
+        store_row<G, NV, VW>(p, r.i0 + r.il0, cb, lane, head);
+    }
+
+    // ---- 5. the row this CTA leaves unfinished ------------------------------------------------
+    if (g == GROUPS - 1) {
+        int gs = GROUPS;
+        while (gs > 0 && s.tail_row[gs - 1] == r.nrows) --gs;
+        if (lane == 0 && cb == 0) p.carry_row[blockIdx.x] = (gs < GROUPS) ? (r.i0 + r.nrows) : -1;
+        if (gs < GROUPS) {
+            float* crow = p.carry_val + (long long)blockIdx.x * p.carry_ld;
+#pragma unroll
+            for (int v = 0; v < NV; ++v) {
+                const int cv = cb + lane + v * G;
+                if (cv < p.ncolv) {
+                    Vec<VW> sum;
+                    sum.load(&s.tail[gs][(lane + v * G) * VW]);
+                    for (int q = gs + 1; q < GROUPS; ++q) {
+                        Vec<VW> t;
+                        t.load(&s.tail[q][(lane + v * G) * VW]);
+                        sum.add(t);
+                    }
+                    sum.store(crow + (long long)cv * VW);
+                }
+            }
+        }
+    }
+}
+
+template <int G, int NV, int VW, int TG, int U, int FMT>
+__global__ void __launch_bounds__(kMergeThreads, (NV >= 4 ? 2 : 3)) spmm_merge_kernel(const SpmmParams p)
+{
+    using Smem = MergeSmem<G, NV, VW, TG>;
+    __shared__ Smem s;
+
+    TileRange r;
+    if (!merge_tile_setup<Smem, G, TG, FMT>(p, s, r)) return;
+    const int g = threadIdx.x / G;
+    const int lane = threadIdx.x % G;
+
+    for (int cb = 0; cb < p.ncolv; cb += G * NV) {
+        Vec<VW> acc[NV];
+        Vec<VW> head[NV];  // the first row this group finishes is held back until step 4
+#pragma unroll
+        for (int v = 0; v < NV; ++v) {
+            acc[v].zero();
+            head[v].zero();
+        }
+        int i = r.il0;
+        bool dirty = false;
+
+        auto finish_row = [&]() {
+            if (i == r.il0) {
+#pragma unroll
+                for (int v = 0; v < NV; ++v) head[v] = acc[v];
+            } else {
+                store_row<G, NV, VW>(p, r.i0 + i, cb, lane, acc);
+            }
+#pragma unroll
+            for (int v = 0; v < NV; ++v) acc[v].zero();
+            dirty = false;
+            ++i;
+        };
+
+        for (int base = r.jl0; base < r.jl1; base += U) {
+            Vec<VW> bq[U][NV];
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int jj = base + u;
+                if (jj < r.jl1) {
+                    const float* brow = p.B + (long long)s.col[jj] * p.ldb;
+#pragma unroll
+                    for (int v = 0; v < NV; ++v) {
+                        const int cv = cb + lane + v * G;
+                        if (cv < p.ncolv) bq[u][v].load_nc(brow + (long long)cv * VW);
+                        else bq[u][v].zero();
+                    }
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int jj = base + u;
+                if (jj < r.jl1) {
+                    while (jj >= s.rowend[i]) finish_row();  // rowend[nrows] = INT_MAX stops it
+                    const float a = s.val[jj];
+#pragma unroll
+                    for (int v = 0; v < NV; ++v) acc[v].fma(a, bq[u][v]);
+                    dirty = true;
+                }
+            }
+        }
+        while (i < r.il1) finish_row();
+
+        merge_tile_finish<Smem, G, NV, VW>(p, s, r, cb, g, lane, acc, head, dirty);
+        if (cb + G * NV < p.ncolv) __syncthreads();  // tails are rewritten by the next pass
+    }
+}
+
+// Adds the carries to C: the first tile of each run of equal carry_row sums the run in tile
+// order and does C[row] += alpha * sum.  One warp per tile, lanes over column vectors.
+template <int VW>
+__global__ void __launch_bounds__(256) spmm_fixup_kernel(const SpmmParams p, int num_tiles)
+{
+    const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (t >= num_tiles) return;
+    const int row = __ldg(p.carry_row + t);
+    if (row < 0 || row >= p.M) return;
+    if (t > 0 && __ldg(p.carry_row + t - 1) == row) return;
+    int e = t + 1;
+    while (e < num_tiles && __ldg(p.carry_row + e) == row) ++e;
+
+    float* crow = p.C + (long long)row * p.ldc;
+    for (int cv = lane; cv < p.ncolv; cv += 32) {
+        Vec<VW> sum;
+        sum.load(p.carry_val + (long long)t * p.carry_ld + (long long)cv * VW);
+        for (int q = t + 1; q < e; ++q) {
+            Vec<VW> x;
+            x.load(p.carry_val + (long long)q * p.carry_ld + (long long)cv * VW);
+            sum.add(x);
+        }
+        Vec<VW> old;
+        old.load(crow + (long long)cv * VW);
+        sum.add_scaled_to(p.alpha, old).store(crow + (long long)cv * VW);
+    }
+}
+
+}  // namespace csrspmm_b200

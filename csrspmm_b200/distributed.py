@@ -1,0 +1,105 @@
+"""Row-partitioned multi-GPU SpMM: one process per GPU, A and C sharded by rows, B replicated.
+
+The reference is single-GPU (its launchers never select a device, src/host/spmm_launcher.cu), so
+this module has no counterpart there.  Rows of C depend only on the same rows of A and on all
+of B, so the product needs no exchange: the matrix is cut into contiguous row blocks of
+near-equal cost (non-zeros + rows, found by binary search on ``row_ptr`` in the C library), each
+rank keeps its block of A re-based to local offsets (column indices unchanged) and a full copy of
+B that is broadcast ONCE, outside any timed region, and every rank multiplies its block with the
+single-GPU kernels.  C stays sharded.  ``torch.distributed`` (NCCL on GPUs, gloo on CPU for the
+host-logic tests) provides the broadcast, the barrier and the max-over-ranks reduction of times.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+
+import numpy as np
+import torch
+
+from . import _lib
+
+
+def partition_rows(row_ptr, parts: int, row_weight: float = 1.0) -> np.ndarray:
+    """bounds[g] .. bounds[g+1] = rows of part g.  ``row_ptr`` is a host array/tensor.  The cost of
+    a row is its nnz + row_weight: with the default weight a row of C written counts like a
+    row of B read, which is what the traffic is."""
+    rp = np.ascontiguousarray(row_ptr.cpu().numpy() if isinstance(row_ptr, torch.Tensor) else row_ptr,
+                              dtype=np.int32)
+    bounds = np.zeros(parts + 1, np.int32)
+    st = _lib.lib().csrspmm_b200_partition_rows(rp.shape[0] - 1, rp.ctypes.data, int(parts), float(row_weight),
+                                                bounds.ctypes.data)
+    _lib.check(st, "csrspmm_b200_partition_rows")
+    return bounds
+
+
+@dataclass
+class Shard:
+    """Rows [row_lo, row_hi) of A with offsets re-based to zero; column indices untouched."""
+    rank: int
+    world: int
+    row_lo: int
+    row_hi: int
+    row_ptr: object
+    col_idx: object
+    values: object
+    max_row_nnz: int
+
+    @property
+    def rows(self) -> int:
+        return self.row_hi - self.row_lo
+
+    @property
+    def nnz(self) -> int:
+        return int(self.col_idx.shape[0])
+
+
+def take_shard(row_ptr, col_idx, values, bounds, rank: int) -> Shard:
+    """Slice of a CSR matrix (numpy arrays or torch tensors on any device) for one rank."""
+    lo, hi = int(bounds[rank]), int(bounds[rank + 1])
+    rp = row_ptr[lo:hi + 1]
+    j0, j1 = int(rp[0]), int(rp[-1])
+    local_rp = rp - rp[0]
+    if isinstance(local_rp, torch.Tensor):
+        local_rp = local_rp.to(torch.int32).contiguous()
+        lens = local_rp[1:] - local_rp[:-1]
+        mx = int(lens.max().item()) if hi > lo else 0
+        ci, va = col_idx[j0:j1].contiguous(), values[j0:j1].contiguous()
+    else:
+        local_rp = np.ascontiguousarray(local_rp, dtype=np.int32)
+        mx = int(np.diff(local_rp).max()) if hi > lo else 0
+        ci, va = np.ascontiguousarray(col_idx[j0:j1]), np.ascontiguousarray(values[j0:j1])
+    return Shard(rank, len(bounds) - 1, lo, hi, local_rp, ci, va, mx)
+
+
+def replicate(t: torch.Tensor, src: int = 0) -> torch.Tensor:
+    """Broadcast a tensor that every rank has already allocated with the same shape."""
+    import torch.distributed as dist
+    if dist.is_initialized() and dist.get_world_size() > 1:
+        dist.broadcast(t, src=src)
+    return t
+
+
+def max_over_ranks(seconds: float, device) -> float:
+    """Job time of a step that every rank timed on its own device."""
+    import torch.distributed as dist
+    t = torch.tensor([seconds], dtype=torch.float64, device=device)
+    if dist.is_initialized() and dist.get_world_size() > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def sum_over_ranks(value: float, device) -> float:
+    import torch.distributed as dist
+    t = torch.tensor([value], dtype=torch.float64, device=device)
+    if dist.is_initialized() and dist.get_world_size() > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.SUM)
+    return float(t.item())
+
+
+def partition_imbalance(row_ptr, bounds, row_weight: float = 1.0) -> float:
+    """max part cost / mean part cost (1.0 = perfect)."""
+    rp = np.asarray(row_ptr.cpu().numpy() if isinstance(row_ptr, torch.Tensor) else row_ptr, dtype=np.int64)
+    b = np.asarray(bounds, dtype=np.int64)
+    cost = (rp[b[1:]] - rp[b[:-1]]) + row_weight * (b[1:] - b[:-1])
+    return float(cost.max() / max(cost.mean(), 1e-30))

@@ -1,0 +1,284 @@
+"""Torch-tensor face of the C ABI: the five ops of the reference's ``torch_csrspmm`` package plus
+a general ``spmm`` with in-place C, strides, packed e2m1 values and a pinned kernel.
+
+The reference's ops are pybind wrappers that fill the two POD views from ``data_ptr()`` and call
+``csrspmm::launch_*`` on the legacy default stream without a device guard
+(torch_csrspmm/torch_csrspmm_naive.cpp:11-58 and its four siblings).  Here the same arguments go
+through ``csrspmm_b200_spmm`` on torch's *current* stream of the tensors' device, and a failed
+call raises instead of returning an unwritten C.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from . import _lib
+
+_ENTRY = {
+    "naive": _lib.ENTRY_NAIVE,
+    "naive_smem": _lib.ENTRY_NAIVE_SMEM,
+    "warp_per_row": _lib.ENTRY_WARP_PER_ROW,
+    "warp_per_row_fp4": _lib.ENTRY_WARP_PER_ROW_FP4,
+    "warp_per_row_smem": _lib.ENTRY_WARP_PER_ROW_SMEM,
+    "warp_per_row_smem_fp4": _lib.ENTRY_WARP_PER_ROW_SMEM_FP4,
+}
+
+
+def _check_csr(row_ptr, col_idx, values, B, packed: bool):
+    # same wording as the reference's TORCH_CHECKs (torch_csrspmm/torch_csrspmm_naive.cpp:19-26)
+    if not row_ptr.is_cuda:
+        raise RuntimeError("A_row_ptr must be a CUDA tensor")
+    if not col_idx.is_cuda:
+        raise RuntimeError("A_col_idx must be a CUDA tensor")
+    if not values.is_cuda:
+        raise RuntimeError("A_values must be a CUDA tensor")
+    if not B.is_cuda:
+        raise RuntimeError("B must be a CUDA tensor")
+    if row_ptr.dtype != torch.int32:
+        raise RuntimeError("A_row_ptr must be int32")
+    if col_idx.dtype != torch.int32:
+        raise RuntimeError("A_col_idx must be int32")
+    if packed:
+        if values.dtype != torch.uint8:
+            raise RuntimeError("packed A_values must be uint8")
+    elif values.dtype != torch.float32:
+        raise RuntimeError("A_values must be float32")
+    if B.dtype != torch.float32:
+        raise RuntimeError("B must be float32")
+    if B.dim() != 2 or row_ptr.dim() != 1 or col_idx.dim() != 1 or values.dim() != 1 or row_ptr.numel() < 1:
+        raise RuntimeError("expected 1-D row_ptr/col_idx/values and 2-D B")
+    if not (row_ptr.is_contiguous() and col_idx.is_contiguous() and values.is_contiguous()):
+        raise RuntimeError("row_ptr, col_idx and values must be contiguous")
+    if B.stride(1) != 1 and B.size(1) > 1:
+        raise RuntimeError("B must be row-major (unit stride along its columns)")
+    dev = B.device
+    if not (row_ptr.device == dev and col_idx.device == dev and values.device == dev):
+        raise RuntimeError("all tensors must be on the same device")
+
+
+def workspace_bytes(M: int, Kd: int, Nd: int, nnz: int) -> int:
+    """Scratch the split kernels need for a problem of these sizes."""
+    a = _lib.make_args(M, Kd, Nd, nnz)
+    return int(_lib.lib().csrspmm_b200_workspace_bytes(C.byref(a)))
+
+
+def spmm(row_ptr, col_idx, values, B, C_out=None, alpha=1.0, beta=0.0, *, entry="naive", kernel="auto",
+         max_row_nnz=0, e2m1_scale=None, nnz=None, workspace=None, status_word=None, sync=False):
+    """C_out = alpha * A @ B + beta * C_out on the current stream; returns C_out.
+
+    C_out is allocated (uninitialised) when omitted, which requires beta == 0.  With
+    ``e2m1_scale`` set, ``values`` holds packed 4-bit codes (uint8, two per byte) and ``nnz``
+    gives the element count.  ``kernel`` pins "row", "merge" or "tma".  ``workspace`` is an
+    optional uint8 tensor of at least ``workspace_bytes(...)`` bytes; without it the scratch comes
+    from torch's caching allocator.  ``sync=True`` waits and raises on device-side errors.
+    """
+    packed = e2m1_scale is not None
+    _check_csr(row_ptr, col_idx, values, B, packed)
+    M = row_ptr.numel() - 1
+    Kd, Nd = B.size(0), B.size(1)
+    n = int(col_idx.numel() if nnz is None else nnz)
+    if not packed and values.numel() != n:
+        raise RuntimeError("values and col_idx differ in length")
+    if packed and values.numel() < (n + 1) // 2:
+        raise RuntimeError("packed values too short")
+    if C_out is None:
+        if beta != 0.0:
+            raise RuntimeError("beta != 0 needs C_out")
+        C_out = torch.empty((M, Nd), dtype=torch.float32, device=B.device)
+    else:
+        if not C_out.is_cuda or C_out.dtype != torch.float32 or C_out.shape != (M, Nd) or C_out.device != B.device:
+            raise RuntimeError("C_out must be a float32 CUDA tensor of shape (M, Nd) on B's device")
+        if C_out.stride(1) != 1 and Nd > 1:
+            raise RuntimeError("C_out must be row-major")
+    L = _lib.lib()
+    ldb = B.stride(0) if Kd > 1 else Nd
+    ldc = C_out.stride(0) if M > 1 else Nd
+    a = _lib.make_args(M, Kd, Nd, n, row_ptr.data_ptr(), col_idx.data_ptr(), values.data_ptr(), B.data_ptr(),
+                       C_out.data_ptr(), ldb=max(ldb, Nd), ldc=max(ldc, Nd), alpha=alpha, beta=beta,
+                       entry=_ENTRY[entry] if isinstance(entry, str) else int(entry),
+                       kernel=_lib.KERNEL_IDS[kernel] if isinstance(kernel, str) else int(kernel),
+                       max_row_nnz=max_row_nnz,
+                       value_format=_lib.VALUES_E2M1 if packed else _lib.VALUES_F32,
+                       value_scale=float(e2m1_scale) if packed else 1.0,
+                       status_word=status_word.data_ptr() if status_word is not None else 0)
+    with torch.cuda.device(B.device):
+        if M > 0 and Nd > 0:
+            chosen = L.csrspmm_b200_select_kernel(C.byref(a))
+            if chosen < 0:
+                raise _lib.SpmmError(-chosen, "csrspmm_b200_select_kernel")
+            if chosen != _lib.KERNEL_ROW:
+                need = int(L.csrspmm_b200_workspace_bytes(C.byref(a)))
+                if workspace is None or workspace.numel() * workspace.element_size() < need:
+                    workspace = torch.empty(need, dtype=torch.uint8, device=B.device)
+                a.workspace = workspace.data_ptr()
+                a.workspace_bytes = workspace.numel() * workspace.element_size()
+        stream = torch.cuda.current_stream(B.device).cuda_stream
+        fn = L.csrspmm_b200_spmm_sync if sync else L.csrspmm_b200_spmm
+        _lib.check(fn(C.byref(a), C.c_void_p(stream)), "csrspmm_b200_spmm")
+        if workspace is not None:
+            workspace.record_stream(torch.cuda.current_stream(B.device))
+    return C_out
+
+
+class SpmmCall:
+    """A prepared SpMM: argument block, kernel choice and scratch fixed once, so that each call is
+    a single trip through the C ABI.  For tight launch loops (benchmarks, repeated products with the
+    same operands); keeps its tensors alive."""
+
+    def __init__(self, row_ptr, col_idx, values, B, C_out, alpha=1.0, beta=0.0, *, entry="naive", kernel="auto",
+                 max_row_nnz=0, e2m1_scale=None, nnz=None, workspace=None, status_word=None):
+        packed = e2m1_scale is not None
+        _check_csr(row_ptr, col_idx, values, B, packed)
+        M, Kd, Nd = row_ptr.numel() - 1, B.size(0), B.size(1)
+        n = int(col_idx.numel() if nnz is None else nnz)
+        if C_out.shape != (M, Nd) or C_out.dtype != torch.float32 or C_out.device != B.device:
+            raise RuntimeError("C_out must be a float32 CUDA tensor of shape (M, Nd) on B's device")
+        self.device = B.device
+        self.L = _lib.lib()
+        self.args = _lib.make_args(
+            M, Kd, Nd, n, row_ptr.data_ptr(), col_idx.data_ptr(), values.data_ptr(), B.data_ptr(), C_out.data_ptr(),
+            ldb=max(B.stride(0) if Kd > 1 else Nd, Nd), ldc=max(C_out.stride(0) if M > 1 else Nd, Nd), alpha=alpha,
+            beta=beta, entry=_ENTRY[entry], kernel=_lib.KERNEL_IDS[kernel], max_row_nnz=max_row_nnz,
+            value_format=_lib.VALUES_E2M1 if packed else _lib.VALUES_F32,
+            value_scale=float(e2m1_scale) if packed else 1.0,
+            status_word=status_word.data_ptr() if status_word is not None else 0)
+        self.kernel = "row"
+        self.launches = 0
+        if M > 0 and Nd > 0:
+            k = self.L.csrspmm_b200_select_kernel(C.byref(self.args))
+            if k < 0:
+                raise _lib.SpmmError(-k, "csrspmm_b200_select_kernel")
+            self.kernel = _lib.KERNEL_NAMES[k]
+            self.launches = 1 if k == _lib.KERNEL_ROW else 2
+            if k != _lib.KERNEL_ROW:
+                need = int(self.L.csrspmm_b200_workspace_bytes(C.byref(self.args)))
+                if workspace is None or workspace.numel() * workspace.element_size() < need:
+                    workspace = torch.empty(need, dtype=torch.uint8, device=B.device)
+                self.args.workspace = workspace.data_ptr()
+                self.args.workspace_bytes = workspace.numel() * workspace.element_size()
+        self._keep = (row_ptr, col_idx, values, B, C_out, workspace, status_word)
+        self._ref = C.byref(self.args)
+        self.out = C_out
+
+    def __call__(self):
+        """Enqueue on the current stream of the operands' device (which must be the current device)."""
+        st = self.L.csrspmm_b200_spmm(self._ref, C.c_void_p(torch.cuda.current_stream(self.device).cuda_stream))
+        if st != _lib.OK:
+            raise _lib.SpmmError(st, "csrspmm_b200_spmm")
+        return self.out
+
+
+def selected_kernel(M, Kd, Nd, nnz, *, entry="naive", max_row_nnz=0, kernel="auto", aligned=True) -> str:
+    """Name of the kernel AUTO picks for these sizes (host-only, needs no GPU)."""
+    a = _lib.make_args(M, Kd, Nd, nnz, B=256 if aligned else 4, Cptr=256 if aligned else 4,
+                       entry=_ENTRY[entry], kernel=_lib.KERNEL_IDS[kernel], max_row_nnz=max_row_nnz)
+    k = _lib.lib().csrspmm_b200_select_kernel(C.byref(a))
+    if k < 0:
+        raise _lib.SpmmError(-k, "csrspmm_b200_select_kernel")
+    return _lib.KERNEL_NAMES[k]
+
+
+# ---- the reference's five ops (torch_csrspmm/__init__.py:10-23): new C = alpha * A @ B ---------------
+# The reference allocates C as zeros when beta != 0 and computes alpha*A*B + beta*0
+# (torch_csrspmm/torch_csrspmm_naive.cpp:32-34); the product with zero is skipped here, which
+# changes nothing but the sign of an exact zero.
+
+def _op(entry, row_ptr, col_idx, values, B, alpha, beta, max_row_nnz=0):
+    del beta
+    return spmm(row_ptr, col_idx, values, B, None, float(alpha), 0.0, entry=entry, max_row_nnz=int(max_row_nnz))
+
+
+def csrspmm_naive(A_rowptr, A_colidx, A_values, B, alpha, beta):
+    return _op("naive", A_rowptr, A_colidx, A_values, B, alpha, beta)
+
+
+def csrspmm_warp_per_row(A_rowptr, A_colidx, A_values, B, alpha, beta):
+    return _op("warp_per_row", A_rowptr, A_colidx, A_values, B, alpha, beta)
+
+
+def csrspmm_warp_per_row_smem(A_rowptr, A_colidx, A_values, A_max_row_nnz, B, alpha, beta):
+    return _op("warp_per_row_smem", A_rowptr, A_colidx, A_values, B, alpha, beta, A_max_row_nnz)
+
+
+def csrspmm_warp_per_row_fp4(A_rowptr, A_colidx, A_values, B, alpha, beta):
+    return _op("warp_per_row_fp4", A_rowptr, A_colidx, A_values, B, alpha, beta)
+
+
+def csrspmm_warp_per_row_smem_fp4(A_rowptr, A_colidx, A_values, A_max_row_nnz, B, alpha, beta):
+    return _op("warp_per_row_smem_fp4", A_rowptr, A_colidx, A_values, B, alpha, beta, A_max_row_nnz)
+
+
+# ---- helpers over the host-only / utility entry points -----------------------------------------------
+
+def e2m1_quantize(values_f32):
+    """Host fp32 tensor/array -> (packed uint8 CPU tensor, scale) with the library's codec."""
+    import numpy as np
+    v = np.ascontiguousarray(values_f32.detach().cpu().numpy() if isinstance(values_f32, torch.Tensor)
+                             else values_f32, dtype=np.float32)
+    L = _lib.lib()
+    scale = float(L.csrspmm_b200_e2m1_scale(v.shape[0], v.ctypes.data))
+    packed = np.zeros((v.shape[0] + 1) // 2, np.uint8)
+    _lib.check(L.csrspmm_b200_e2m1_encode(v.shape[0], v.ctypes.data, scale, packed.ctypes.data), "e2m1_encode")
+    return torch.from_numpy(packed), scale
+
+
+def e2m1_dequantize(packed, n, scale):
+    import numpy as np
+    pk = np.ascontiguousarray(packed.cpu().numpy() if isinstance(packed, torch.Tensor) else packed, dtype=np.uint8)
+    out = np.empty(int(n), np.float32)
+    _lib.check(_lib.lib().csrspmm_b200_e2m1_decode(int(n), pk.ctypes.data, float(scale), out.ctypes.data),
+               "e2m1_decode")
+    return torch.from_numpy(out)
+
+
+def validate_csr(row_ptr, col_idx, Kd: int) -> int:
+    """Checks a CSR structure (host or CUDA int32 tensors); returns the problem bits and raises
+    SpmmError(ERR_INVALID_CSR) when the matrix cannot be multiplied safely."""
+    M = row_ptr.numel() - 1
+    flags = C.c_uint32(0)
+    L = _lib.lib()
+    if row_ptr.is_cuda:
+        with torch.cuda.device(row_ptr.device):
+            st = L.csrspmm_b200_validate_csr_device(M, Kd, col_idx.numel(), row_ptr.data_ptr(), col_idx.data_ptr(),
+                                                    C.byref(flags),
+                                                    C.c_void_p(torch.cuda.current_stream(row_ptr.device).cuda_stream))
+    else:
+        st = L.csrspmm_b200_validate_csr_host(M, Kd, col_idx.numel(), row_ptr.data_ptr(), col_idx.data_ptr(),
+                                              C.byref(flags))
+    _lib.check(st, "csrspmm_b200_validate_csr")
+    return int(flags.value)
+
+
+def row_stats(row_ptr) -> dict:
+    """Longest row, empty rows, rows longer than 32*(mean+1) and their nnz, from a CUDA row_ptr."""
+    out = (C.c_int64 * 4)()
+    with torch.cuda.device(row_ptr.device):
+        st = _lib.lib().csrspmm_b200_row_stats_device(row_ptr.numel() - 1, row_ptr.data_ptr(), out,
+                                                      C.c_void_p(torch.cuda.current_stream(row_ptr.device).cuda_stream))
+    _lib.check(st, "csrspmm_b200_row_stats_device")
+    return dict(max_row_nnz=int(out[0]), empty_rows=int(out[1]), long_rows=int(out[2]), long_rows_nnz=int(out[3]))
+
+
+def spmm_host(row_ptr, col_idx, values, B, C_host, alpha=1.0, beta=0.0, *, entry="naive", kernel="auto",
+              max_row_nnz=0, arena=None, device=None):
+    """End-to-end call on HOST tensors (ideally pinned): copies A and B in, multiplies, copies C
+    back into C_host and waits.  ``arena`` is an optional CUDA uint8 tensor to stage in."""
+    M = row_ptr.numel() - 1
+    Kd, Nd = B.shape
+    a = _lib.make_args(M, Kd, Nd, col_idx.numel(), row_ptr.data_ptr(), col_idx.data_ptr(), values.data_ptr(),
+                       B.data_ptr(), C_host.data_ptr(), ldb=B.stride(0) if Kd > 1 else Nd,
+                       ldc=C_host.stride(0) if M > 1 else Nd, alpha=alpha, beta=beta, entry=_ENTRY[entry],
+                       kernel=_lib.KERNEL_IDS[kernel], max_row_nnz=max_row_nnz)
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    with torch.cuda.device(dev):
+        stream = torch.cuda.current_stream(dev).cuda_stream
+        st = _lib.lib().csrspmm_b200_spmm_host(C.byref(a), arena.data_ptr() if arena is not None else None,
+                                               arena.numel() if arena is not None else 0, C.c_void_p(stream))
+    _lib.check(st, "csrspmm_b200_spmm_host")
+    return C_host
+
+
+def host_arena_bytes(M, Kd, Nd, nnz) -> int:
+    a = _lib.make_args(M, Kd, Nd, nnz)
+    return int(_lib.lib().csrspmm_b200_host_arena_bytes(C.byref(a)))

@@ -1,0 +1,174 @@
+/*
+ * csrspmm_b200 -- C ABI of the sm_100a CSR x dense SpMM kernel library.
+ *
+ *     C[M x Nd] = alpha * A[M x Kd, CSR] * B[Kd x Nd] + beta * C        (fp32, int32 indices,
+ *                                                                        row-major dense)
+ *
+ * This is the boundary the reference's host layer would bind instead of launching its own
+ * src/device kernels.  Plain pointers and sizes only: no C++ types, no exceptions, no exit().
+ * Every function returns a csrspmm_b200_status (0 = ok) unless stated otherwise.
+ *
+ * What each entry point stands in for in the reference (paths within the reference project):
+ *   csrspmm_b200_spmm           the six launchers src/host/spmm_launcher.cu:11-171 and the
+ *                               kernels they start (src/device/csrspmm_naive.cu:11-39,
+ *                               csrspmm_naive_smem.cu:5-44, csrspmm_warp_per_row.cu:13-48,
+ *                               csrspmm_warp_per_row_fp4.cu:9-65,
+ *                               csrspmm_warp_per_row_smem.cu:11-62,
+ *                               csrspmm_warp_per_row_smem_fp4.cu:11-84)
+ *   csrspmm_b200_spmm_sync      csrspmm::spmm, src/csrspmm.cpp:28-75 (launch, then
+ *                               cudaGetLastError + cudaDeviceSynchronize)
+ *   csrspmm_b200_spmm_host      the host round trip the reference's callers spell out by hand:
+ *                               csr_host2device / dense_host2device / spmm / dense_device2host
+ *                               (tests/test_csrspmm.cu:80-92, benchmarks/bench_csrspmm.cu:84-91)
+ *   csrspmm_b200_select_kernel  the (stub) auto-selection in src/csrspmm.cpp:34-40
+ *   validate / row_stats / partition_rows / e2m1_*   no counterpart in the reference
+ */
+#ifndef CSRSPMM_B200_H
+#define CSRSPMM_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define CSRSPMM_B200_ABI_VERSION 1
+
+/* Same handle type as cudaStream_t; NULL is the legacy default stream. */
+typedef struct CUstream_st* csrspmm_b200_stream_t;
+
+typedef enum csrspmm_b200_status {
+    CSRSPMM_B200_OK = 0,
+    CSRSPMM_B200_ERR_BAD_ARG = 1,      /* null pointer, negative size, bad enum, bad struct_size */
+    CSRSPMM_B200_ERR_INVALID_CSR = 2,  /* validation found a malformed matrix */
+    CSRSPMM_B200_ERR_UNSUPPORTED = 3,  /* a forced kernel cannot run this shape/alignment */
+    CSRSPMM_B200_ERR_CUDA = 4,         /* a CUDA call failed; see csrspmm_b200_last_error */
+    CSRSPMM_B200_ERR_DEVICE_WAIT = 5,  /* a bounded device-side wait gave up (status word set) */
+    CSRSPMM_B200_ERR_WORKSPACE = 6,    /* caller's workspace is too small or misaligned */
+    CSRSPMM_B200_ERR_NO_DEVICE = 7     /* no usable sm_100 device */
+} csrspmm_b200_status;
+
+/* Which of the reference's entry points the caller is serving (same order as
+ * csrspmm::Algorithm, include/csrspmm/csrspmm.h:10-17).  It is a hint for kernel selection;
+ * every value computes the same C. */
+typedef enum csrspmm_b200_entry {
+    CSRSPMM_B200_ENTRY_NAIVE = 0,
+    CSRSPMM_B200_ENTRY_NAIVE_SMEM = 1,
+    CSRSPMM_B200_ENTRY_WARP_PER_ROW = 2,
+    CSRSPMM_B200_ENTRY_WARP_PER_ROW_FP4 = 3,
+    CSRSPMM_B200_ENTRY_WARP_PER_ROW_SMEM = 4,
+    CSRSPMM_B200_ENTRY_WARP_PER_ROW_SMEM_FP4 = 5
+} csrspmm_b200_entry;
+
+typedef enum csrspmm_b200_kernel {
+    CSRSPMM_B200_KERNEL_AUTO = 0,
+    CSRSPMM_B200_KERNEL_ROW = 1,    /* lane group per row; sequential accumulation per output */
+    CSRSPMM_B200_KERNEL_MERGE = 2,  /* merge-path split over (rows + nnz); carries + fix-up */
+    CSRSPMM_B200_KERNEL_TMA = 3     /* merge-path split, B rows staged through shared memory by
+                                       bulk async copies (needs the 16-byte-aligned layout) */
+} csrspmm_b200_kernel;
+
+typedef enum csrspmm_b200_value_format {
+    CSRSPMM_B200_VALUES_F32 = 0,
+    CSRSPMM_B200_VALUES_E2M1 = 1 /* two 4-bit codes per byte, element j in byte j/2 (even j = low
+                                    nibble); value = magnitude(code) * value_scale */
+} csrspmm_b200_value_format;
+
+/* All pointers are DEVICE pointers (csrspmm_b200_spmm, _sync) or HOST pointers (_spmm_host). */
+typedef struct csrspmm_b200_args {
+    uint32_t struct_size; /* sizeof(csrspmm_b200_args), checked */
+    int32_t M;            /* rows of A and C */
+    int32_t Kd;           /* columns of A = rows of B */
+    int32_t Nd;           /* columns of B and C */
+    int64_t nnz;          /* stored non-zeros, < 2^31 */
+    const int32_t* row_ptr; /* M + 1 */
+    const int32_t* col_idx; /* nnz */
+    const void* values;     /* nnz floats, or (nnz+1)/2 bytes for E2M1 */
+    int32_t value_format;   /* csrspmm_b200_value_format */
+    float value_scale;      /* E2M1 only */
+    const float* B;
+    int64_t ldb; /* elements between consecutive rows of B; the reference's layout is ldb == Nd */
+    float* C;
+    int64_t ldc;
+    float alpha;
+    float beta;         /* C is not read when beta == 0 */
+    int32_t entry;      /* csrspmm_b200_entry */
+    int32_t kernel;     /* csrspmm_b200_kernel; AUTO unless pinned */
+    int32_t max_row_nnz; /* longest row if known, else 0 (a hint, never trusted for bounds) */
+    int32_t reserved0;
+    void* workspace;        /* device scratch for the split kernels, or NULL: the library then
+                               takes it from the stream-ordered allocator for this call */
+    size_t workspace_bytes; /* size of workspace when it is not NULL */
+    int32_t* status_word;   /* optional device int32 the kernels OR error bits into */
+} csrspmm_b200_args;
+
+int csrspmm_b200_abi_version(void);
+const char* csrspmm_b200_status_string(int status);
+/* Text of the most recent failure on the calling thread ("" if none). */
+const char* csrspmm_b200_last_error(void);
+
+/* Asynchronous: enqueue the SpMM on `stream` and return.  Device pointers. */
+int csrspmm_b200_spmm(const csrspmm_b200_args* args, csrspmm_b200_stream_t stream);
+
+/* As above, then wait for the stream and report launch/execution errors and the status word. */
+int csrspmm_b200_spmm_sync(const csrspmm_b200_args* args, csrspmm_b200_stream_t stream);
+
+/* Host pointers in `args` (workspace/status_word ignored).  Copies A and B (and C when
+ * beta != 0) to the current device, runs the SpMM, copies C back and waits.  When
+ * device_arena is NULL the device buffers are allocated and released inside the call; else
+ * the arena (>= csrspmm_b200_host_arena_bytes(args) bytes, 256-byte aligned) is used. */
+int csrspmm_b200_spmm_host(const csrspmm_b200_args* args, void* device_arena,
+                           size_t device_arena_bytes, csrspmm_b200_stream_t stream);
+size_t csrspmm_b200_host_arena_bytes(const csrspmm_b200_args* args);
+
+/* Scratch the split kernels need for this problem (0 for the row kernel).  Depends only on
+ * sizes, never on matrix contents. */
+size_t csrspmm_b200_workspace_bytes(const csrspmm_b200_args* args);
+
+/* The kernel AUTO resolves to for these arguments (host-only logic, no CUDA call);
+ * returns a csrspmm_b200_kernel, or a negative csrspmm_b200_status on bad arguments.
+ * The environment variable CSRSPMM_FORCE_KERNEL=row|merge|tma overrides AUTO. */
+int csrspmm_b200_select_kernel(const csrspmm_b200_args* args);
+
+/* ---- CSR validation (new; the reference validates nothing) ---------------------------------- */
+
+#define CSRSPMM_B200_CSR_BAD_ROWPTR0 1u    /* row_ptr[0] != 0 */
+#define CSRSPMM_B200_CSR_BAD_ROWPTR_END 2u /* row_ptr[M] != nnz */
+#define CSRSPMM_B200_CSR_NOT_MONOTONE 4u   /* row_ptr[i+1] < row_ptr[i] */
+#define CSRSPMM_B200_CSR_COL_RANGE 8u      /* col_idx[j] < 0 or >= Kd */
+#define CSRSPMM_B200_CSR_COL_UNSORTED 16u  /* columns of a row not strictly ascending (allowed
+                                              by the kernels; reported, not an error) */
+
+/* Host arrays.  *problems receives the OR of the bits above.  Returns ERR_INVALID_CSR when any
+ * of the first four bits is set. */
+int csrspmm_b200_validate_csr_host(int32_t M, int32_t Kd, int64_t nnz, const int32_t* row_ptr,
+                                   const int32_t* col_idx, uint32_t* problems);
+/* Device arrays; runs a checking kernel on `stream` and waits for it. */
+int csrspmm_b200_validate_csr_device(int32_t M, int32_t Kd, int64_t nnz, const int32_t* row_ptr,
+                                     const int32_t* col_idx, uint32_t* problems,
+                                     csrspmm_b200_stream_t stream);
+
+/* Device row_ptr -> stats[0] = longest row, stats[1] = empty rows, stats[2] = rows longer than
+ * 32 * (mean + 1), stats[3] = nnz held by those rows.  Waits for the stream. */
+int csrspmm_b200_row_stats_device(int32_t M, const int32_t* row_ptr, int64_t stats[4],
+                                  csrspmm_b200_stream_t stream);
+
+/* ---- multi-GPU row partition (new) ------------------------------------------------------------
+ * Contiguous row blocks [bounds[g], bounds[g+1]) for g < parts with near-equal cost, where the
+ * cost of a row is its nnz + row_weight (row_weight = 1 balances B-row reads against C-row
+ * writes; 0 balances nnz alone).  Host row_ptr.  A row is never split. */
+int csrspmm_b200_partition_rows(int32_t M, const int32_t* row_ptr, int32_t parts,
+                                double row_weight, int32_t* bounds);
+
+/* ---- e2m1 value codec (new; the reference's "Fp4" kernels take fp32 values) -------------------
+ * Host buffers.  scale = max|v| / 6 (1 when all zero); encode rounds v/scale to the nearest of
+ * {0, .5, 1, 1.5, 2, 3, 4, 6}, ties to the even code, saturating, sign kept. */
+float csrspmm_b200_e2m1_scale(int64_t n, const float* values);
+int csrspmm_b200_e2m1_encode(int64_t n, const float* values, float scale, uint8_t* packed);
+int csrspmm_b200_e2m1_decode(int64_t n, const uint8_t* packed, float scale, float* values);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CSRSPMM_B200_H */

@@ -1,0 +1,22 @@
+import sys
+from pathlib import Path
+
+import pytest
+
+ROOT = Path(__file__).resolve().parents[1]
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+
+def pytest_configure(config):
+    config.addinivalue_line("markers", "gpu: needs a CUDA device (run with -m gpu on a B200)")
+
+
+@pytest.fixture(scope="session")
+def cuda_lib():
+    """The kernel library on a real GPU.  Fails (never skips) when either is missing: a GPU test
+    that silently ran something else would prove nothing."""
+    import torch
+    from csrspmm_b200 import _lib
+    assert torch.cuda.is_available(), "GPU test started without a CUDA device"
+    return _lib.lib()

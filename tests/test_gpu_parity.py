@@ -1,0 +1,395 @@
+"""Parity of the CUDA kernels with the CPU oracle, through the C ABI (csrspmm_b200_spmm).
+
+Tolerances (fp32 path): a row that one lane group accumulates from start to end must equal the
+sequential fused oracle bit for bit (always the case for the row kernel); everything must satisfy
+rtol 1e-5 / atol 1e-6 against it, except rows that the split kernels cut into pieces, which
+are judged against the fp64 oracle with |err| <= 1e-5 * sum|a*b| + 1e-6.
+"""
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from csrspmm_b200 import _lib, generators as G, ops
+
+pytestmark = pytest.mark.gpu
+
+GOLDEN = Path(__file__).resolve().parent / "golden"
+SMALL = sorted(p.stem for p in GOLDEN.glob("*.npz") if p.stem != "cfg1_check")
+KERNELS = ["row", "merge", "tma"]
+ENTRIES = ["naive", "naive_smem", "warp_per_row", "warp_per_row_fp4", "warp_per_row_smem", "warp_per_row_smem_fp4"]
+RTOL, ATOL = 1e-5, 1e-6
+
+
+def dev(x):
+    return torch.from_numpy(np.ascontiguousarray(x)).cuda()
+
+
+def tma_ok(Nd):
+    return Nd % 4 == 0 and 4 <= Nd <= 512
+
+
+def run(p_or_arrays, kernel="auto", C0=None, alpha=1.0, beta=0.0, entry="naive", max_row_nnz=0, **kw):
+    rp, ci, va, B = p_or_arrays
+    Cd = dev(C0) if C0 is not None else None
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    out = ops.spmm(dev(rp), dev(ci), dev(va), dev(B), Cd, alpha, beta, entry=entry, kernel=kernel,
+                   max_row_nnz=max_row_nnz, status_word=status, sync=True, **kw)
+    assert int(status.item()) == 0
+    return out.cpu().numpy()
+
+
+def assert_parity(got, rp, ci, va, B, C0=None, alpha=1.0, beta=0.0, exact=False):
+    want = oracle.spmm(rp, ci, va, B, C0, alpha, beta, fused=True, threads=4)
+    if exact:
+        assert np.array_equal(got, want), f"max diff {np.abs(got - want).max()}"
+        return
+    f64, mag = oracle.spmm_f64(rp, ci, va, B, C0, alpha, beta, threads=4)
+    err = np.abs(got.astype(np.float64) - f64)
+    assert (err <= RTOL * mag + ATOL).all(), f"worst excess {(err - RTOL * mag - ATOL).max()}"
+    close = np.isclose(got, want, rtol=RTOL, atol=ATOL)
+    # only elements of rows cut into pieces may miss the elementwise tolerance
+    assert close.mean() > 0.999, f"elementwise pass rate {close.mean()}"
+
+
+def arrays(p):
+    return p.row_ptr, p.col_idx, p.values, p.B
+
+
+# ---- golden vectors produced by the reference's own host code ---------------------------------------
+
+@pytest.mark.parametrize("kernel", KERNELS)
+@pytest.mark.parametrize("name", SMALL)
+def test_golden_small(cuda_lib, name, kernel):
+    g = np.load(GOLDEN / f"{name}.npz")
+    Nd = g["B"].shape[1]
+    if kernel == "tma" and not tma_ok(Nd):
+        pytest.skip("layout not eligible for the TMA kernel")
+    alpha, beta = float(g["alpha"]), float(g["beta"])
+    a = (g["row_ptr"], g["col_idx"], g["values"], g["B"])
+    got = run(a, kernel, g["C0"], alpha, beta)
+    np.testing.assert_allclose(got, g["expect"], rtol=1e-5, atol=2e-5)  # reference sums unfused
+    assert_parity(got, *a, g["C0"], alpha, beta, exact=(kernel == "row"))
+
+
+@pytest.mark.parametrize("kernel", KERNELS)
+def test_golden_cfg1(cuda_lib, kernel):
+    g = np.load(GOLDEN / "cfg1_check.npz")
+    p = G.make("cfg1_check")
+    got = run(arrays(p), kernel)
+    np.testing.assert_allclose(got, g["expect_ab"], rtol=RTOL, atol=ATOL)
+    assert_parity(got, *arrays(p), exact=(kernel == "row"))
+    C0 = np.random.default_rng(1000).standard_normal((p.M, p.Nd), dtype=np.float32)
+    got = run(arrays(p), kernel, C0, 1.0, 0.5)
+    np.testing.assert_allclose(got, g["expect_half"], rtol=RTOL, atol=ATOL)
+
+
+# ---- every entry point of the reference ------------------------------------------------------------
+
+@pytest.mark.parametrize("entry", ENTRIES)
+def test_entry_points_cfg1(cuda_lib, entry):
+    p = G.make("cfg1_check")
+    mx = int(np.diff(p.row_ptr).max())
+    got = run(arrays(p), "auto", entry=entry, max_row_nnz=mx)
+    assert_parity(got, *arrays(p))
+    got0 = run(arrays(p), "auto", entry=entry, max_row_nnz=0)  # hint absent, as the torch ops leave it
+    assert_parity(got0, *arrays(p))
+
+
+def test_torch_ops_match_reference_test_protocol(cuda_lib):
+    # shapes and checks of the reference's tests/test_pytorch.py:41-105 (alpha = beta = 1, result = A @ B)
+    import torch_csrspmm as T
+    rng = np.random.default_rng(0)
+    shapes = [(4, 4, 8), (8, 8, 16)] + [(2 ** int(a), 2 ** int(b), 2 ** int(c)) for a, b, c in rng.integers(2, 11, (5, 3))]
+    for M, N, K in shapes:
+        p = G.random_csr(M, N, K, 0.3, seed=M * 7 + N, vlo=0.0, vhi=1.0)
+        rp, ci, va, B = (dev(x) for x in arrays(p))
+        mx = int(np.diff(p.row_ptr).max()) if M else 0
+        A = torch.from_numpy(oracle.csr2dense(M, N, p.row_ptr, p.col_idx, p.values)).cuda()
+        want = A @ B
+        outs = [T.csrspmm_naive(rp, ci, va, B, 1, 1), T.csrspmm_warp_per_row(rp, ci, va, B, 1, 1),
+                T.csrspmm_warp_per_row_smem(rp, ci, va, mx, B, 1, 1), T.csrspmm_warp_per_row_fp4(rp, ci, va, B, 1, 1),
+                T.csrspmm_warp_per_row_smem_fp4(rp, ci, va, mx, B, 1, 1)]
+        for o in outs:
+            assert o.shape == (M, K) and o.dtype == torch.float32 and o.is_cuda
+            assert torch.allclose(o, want, atol=1e-4, rtol=1e-4)
+            assert_parity(o.cpu().numpy(), *arrays(p))
+
+
+def test_torch_op_argument_checks(cuda_lib):
+    import torch_csrspmm as T
+    p = G.random_csr(8, 8, 8, 0.5, seed=1)
+    rp, ci, va, B = (dev(x) for x in arrays(p))
+    with pytest.raises(RuntimeError, match="A_row_ptr must be int32"):
+        T.csrspmm_naive(rp.long(), ci, va, B, 1, 0)
+    with pytest.raises(RuntimeError, match="A_values must be float32"):
+        T.csrspmm_warp_per_row(rp, ci, va.double(), B, 1, 0)
+    with pytest.raises(RuntimeError, match="B must be a CUDA tensor"):
+        T.csrspmm_warp_per_row_fp4(rp, ci, va, B.cpu(), 1, 0)
+
+
+# ---- shapes the reference's tests never reach ------------------------------------------------------------
+
+@pytest.mark.parametrize("kernel", KERNELS)
+@pytest.mark.parametrize("Nd", [1, 2, 3, 4, 5, 7, 8, 12, 33, 64, 65, 100, 128, 132, 256, 260, 512, 516, 1024, 1100])
+def test_dense_widths(cuda_lib, Nd, kernel):
+    if kernel == "tma" and not tma_ok(Nd):
+        pytest.skip("layout not eligible for the TMA kernel")
+    p = G.random_csr(203, 150, Nd, 0.08, seed=Nd)  # M not a multiple of 4; some empty rows
+    C0 = np.random.default_rng(Nd).standard_normal((p.M, Nd), dtype=np.float32)
+    got = run(arrays(p), kernel, C0, 0.75, -1.25)
+    assert_parity(got, *arrays(p), C0, 0.75, -1.25, exact=(kernel == "row"))
+
+
+@pytest.mark.parametrize("kernel", KERNELS)
+@pytest.mark.parametrize("beta", [0.0, 0.5, 1.0])
+def test_alpha_beta_and_poisoned_c(cuda_lib, kernel, beta):
+    p = G.random_csr(97, 64, 64, 0.2, seed=21)
+    C0 = np.random.default_rng(3).standard_normal((p.M, p.Nd), dtype=np.float32)
+    if beta == 0.0:
+        C0[:] = np.nan  # C must not be read when beta == 0 (src/device/csrspmm_naive.cu:38)
+    got = run(arrays(p), kernel, C0, 1.7, beta)
+    assert np.isfinite(got).all()
+    assert_parity(got, *arrays(p), None if beta == 0.0 else C0, 1.7, beta, exact=(kernel == "row"))
+
+
+@pytest.mark.parametrize("kernel", KERNELS)
+def test_empty_and_degenerate(cuda_lib, kernel):
+    # nnz == 0: C = beta * C
+    p = G.random_csr(37, 20, 16, 0.0, seed=1, lengths=np.zeros(37, np.int64))
+    C0 = np.random.default_rng(1).standard_normal((37, 16), dtype=np.float32)
+    got = run(arrays(p), kernel, C0, 1.0, 2.0)
+    assert np.array_equal(got, 2.0 * C0)
+    got = run(arrays(p), kernel)
+    assert not got.any()
+    # single row, single column of A
+    p = G.random_csr(1, 1, 8, 1.0, seed=2, lengths=np.array([1]))
+    assert_parity(run(arrays(p), kernel), *arrays(p), exact=(kernel == "row"))
+    # M == 0
+    out = ops.spmm(torch.zeros(1, dtype=torch.int32, device="cuda"), torch.zeros(0, dtype=torch.int32, device="cuda"),
+                   torch.zeros(0, device="cuda"), torch.zeros(4, 8, device="cuda"), kernel=kernel)
+    assert out.shape == (0, 8)
+
+
+@pytest.mark.parametrize("kernel", KERNELS)
+def test_rows_longer_than_the_reference_can_stage(cuda_lib, kernel):
+    # 1536 non-zeros per row is where the reference's shared-memory kernels stop launching
+    # (src/host/spmm_launcher.cu:112-120); rows here reach 70000
+    lens = np.array([70000, 0, 3, 5000, 1, 1537, 0, 0, 20000, 2, 1, 0, 9], np.int64)
+    p = G.random_csr(len(lens), 100_000, 64, 0.0, seed=31, lengths=lens)
+    C0 = np.random.default_rng(5).standard_normal((p.M, p.Nd), dtype=np.float32)
+    got = run(arrays(p), kernel, C0, 1.0, 0.5)
+    f64, mag = oracle.spmm_f64(*arrays(p), C0, 1.0, 0.5)
+    assert (np.abs(got - f64) <= RTOL * mag + ATOL).all()
+    if kernel == "row":
+        assert np.array_equal(got, oracle.spmm(*arrays(p), C0, 1.0, 0.5))
+    # wide B too (512 columns: four float4 per lane)
+    p = G.random_csr(5, 30_000, 512, 0.0, seed=32, lengths=np.array([9000, 1, 0, 2500, 40]))
+    got = run(arrays(p), kernel)
+    f64, mag = oracle.spmm_f64(*arrays(p))
+    assert (np.abs(got - f64) <= RTOL * mag + ATOL).all()
+
+
+@pytest.mark.parametrize("kernel", ["row", "merge"])
+def test_strides_and_unaligned_operands(cuda_lib, kernel):
+    p = G.random_csr(61, 47, 24, 0.25, seed=41)
+    rp, ci, va = dev(p.row_ptr), dev(p.col_idx), dev(p.values)
+    want = oracle.spmm(*arrays(p))
+    # B and C as column slices of wider tensors: ldb, ldc > Nd (vector layout still holds)
+    Bw = torch.zeros(p.Kd, 40, device="cuda")
+    Bw[:, 8:32] = dev(p.B)
+    Cw = torch.full((p.M, 36), 7.0, device="cuda")
+    ops.spmm(rp, ci, va, Bw[:, 8:32], Cw[:, 4:28], kernel=kernel, sync=True)
+    got = Cw.cpu().numpy()
+    assert (got[:, :4] == 7.0).all() and (got[:, 28:] == 7.0).all()
+    assert np.allclose(got[:, 4:28], want, rtol=RTOL, atol=ATOL)
+    # base pointers off the 16-byte grid: scalar path
+    Bw = torch.zeros(p.Kd, 25, device="cuda")
+    Bw[:, 1:] = dev(p.B)
+    Cw = torch.zeros(p.M, 25, device="cuda")
+    ops.spmm(rp, ci, va, Bw[:, 1:], Cw[:, 1:], kernel=kernel, sync=True)
+    assert np.allclose(Cw.cpu().numpy()[:, 1:], want, rtol=RTOL, atol=ATOL) and not Cw[:, 0].any()
+
+
+# ---- the BASELINE configurations ---------------------------------------------------------------------
+
+@pytest.mark.parametrize("kernel", KERNELS)
+def test_cfg2_medium_full_size(cuda_lib, kernel):
+    p = G.make("cfg2_medium")
+    got = run(arrays(p), kernel, max_row_nnz=int(np.diff(p.row_ptr).max()))
+    assert_parity(got, *arrays(p), exact=(kernel == "row"))
+
+
+@pytest.mark.parametrize("kernel", KERNELS)
+@pytest.mark.parametrize("name,scale", [("cfg3_powerlaw", 16), ("cfg4_fp4", 16), ("cfg5_xl", 128)])
+def test_scaled_configs(cuda_lib, name, scale, kernel):
+    p = G.make(name, scale=scale)
+    got = run(arrays(p), kernel)
+    assert_parity(got, *arrays(p), exact=(kernel == "row"))
+
+
+def _check_sampled_rows(rp_h, ci_d, va_d, B_d, C_d, rows, alpha=1.0):
+    """Oracle on a sample of rows of a device-resident problem (only the B rows they touch are
+    brought to the host, with the column indices renumbered onto that subset)."""
+    rows = np.unique(np.asarray(rows, np.int64))
+    starts, ends = rp_h[rows].astype(np.int64), rp_h[rows + 1].astype(np.int64)
+    lens = ends - starts
+    idx = np.concatenate([np.arange(s, e) for s, e in zip(starts, ends)]) if lens.sum() else np.zeros(0, np.int64)
+    idx_d = torch.from_numpy(idx).cuda()
+    cols = ci_d[idx_d].long()
+    uniq, inv = torch.unique(cols, return_inverse=True)
+    sub_rp = np.zeros(len(rows) + 1, np.int32)
+    np.cumsum(lens, out=sub_rp[1:])
+    sub_B = B_d[uniq].cpu().numpy()
+    sub_ci, sub_va = inv.to(torch.int32).cpu().numpy(), va_d[idx_d].cpu().numpy()
+    got = C_d[torch.from_numpy(rows).cuda()].cpu().numpy()
+    f64, mag = oracle.spmm_f64(sub_rp, sub_ci, sub_va, sub_B, None, alpha, 0.0, threads=4)
+    assert (np.abs(got - f64) <= RTOL * mag + ATOL).all()
+    want = oracle.spmm(sub_rp, sub_ci, sub_va, sub_B, None, alpha, 0.0, threads=4)
+    return float(np.isclose(got, want, rtol=RTOL, atol=ATOL).mean())
+
+
+def _sample(rp_h, rng, n_random=20000, n_long=64):
+    lens = np.diff(rp_h.astype(np.int64))
+    longest = np.argsort(lens)[-n_long:]
+    return np.concatenate([longest, rng.integers(0, len(lens), n_random), [0, len(lens) - 1]])
+
+
+@pytest.mark.parametrize("kernel", ["merge", "tma"])
+def test_cfg3_powerlaw_full_size(cuda_lib, kernel):
+    """BASELINE config 3 at full size (2^20 rows, ~16.8 M nnz), generated on the device."""
+    p = G.make("cfg3_powerlaw", device="cuda")
+    assert p.M == 1 << 20 and abs(p.nnz / p.M - 16.0) < 0.1
+    rp_h = p.row_ptr.cpu().numpy()
+    assert int(np.diff(rp_h).max()) <= 16384
+    Cd = ops.spmm(p.row_ptr, p.col_idx, p.values, p.B, kernel=kernel, sync=True)
+    rate = _check_sampled_rows(rp_h, p.col_idx, p.values, p.B, Cd, _sample(rp_h, np.random.default_rng(0)))
+    assert rate > 0.999
+    # size-independent properties: linearity in alpha, and with B = 1 every row of C is the row sum of A
+    C2 = ops.spmm(p.row_ptr, p.col_idx, p.values, p.B, None, 2.0, kernel=kernel, sync=True)
+    assert torch.equal(C2, 2.0 * Cd)  # scaling by 2 is exact in binary floating point
+    ones = torch.ones(p.Kd, 64, device="cuda")
+    Cs = ops.spmm(p.row_ptr, p.col_idx, p.values, ones, kernel=kernel, sync=True)
+    csum = torch.zeros(p.nnz + 1, dtype=torch.float64, device="cuda")
+    csum[1:] = torch.cumsum(p.values.double(), 0)
+    rowsum = csum[p.row_ptr[1:].long()] - csum[p.row_ptr[:-1].long()]
+    assert torch.allclose(Cs[:, 0].double(), rowsum, rtol=1e-5, atol=1e-4)
+    assert torch.equal(Cs[:, :1].expand(-1, 64), Cs)  # all columns identical
+    # run-to-run determinism (no atomics on C)
+    assert torch.equal(Cd, ops.spmm(p.row_ptr, p.col_idx, p.values, p.B, kernel=kernel, sync=True))
+
+
+@pytest.mark.parametrize("kernel", ["merge", "tma"])
+def test_cfg5_xl_eighth_size(cuda_lib, kernel):
+    """BASELINE config 5's row-length law and width (Zipf 2.2, mean 32, Nd 512) on 2^19 rows."""
+    p = G.make("cfg5_xl", scale=8, device="cuda")
+    rp_h = p.row_ptr.cpu().numpy()
+    Cd = ops.spmm(p.row_ptr, p.col_idx, p.values, p.B, kernel=kernel, sync=True)
+    rate = _check_sampled_rows(rp_h, p.col_idx, p.values, p.B, Cd, _sample(rp_h, np.random.default_rng(1), 4000, 32))
+    assert rate > 0.999
+    assert torch.equal(Cd, ops.spmm(p.row_ptr, p.col_idx, p.values, p.B, kernel=kernel, sync=True))
+
+
+# ---- e2m1 values -----------------------------------------------------------------------------------
+
+@pytest.mark.parametrize("kernel", KERNELS)
+def test_e2m1_path(cuda_lib, kernel):
+    p = G.make("cfg4_fp4", scale=32)
+    packed, scale = ops.e2m1_quantize(p.values)
+    decoded = oracle.e2m1_decode(packed.numpy(), p.nnz, scale)
+    rp, ci, B = dev(p.row_ptr), dev(p.col_idx), dev(p.B)
+    got = ops.spmm(rp, ci, packed.cuda(), B, kernel=kernel, e2m1_scale=scale, nnz=p.nnz, sync=True)
+    # identical in decoded operands: the packed path must equal the fp32 path fed the decoded values
+    same = ops.spmm(rp, ci, dev(decoded), B, kernel=kernel, sync=True)
+    assert torch.equal(got, same)
+    # and within rel 1e-4 of the oracle on the decoded values
+    want = oracle.spmm(p.row_ptr, p.col_idx, decoded, p.B, threads=4)
+    f64, mag = oracle.spmm_f64(p.row_ptr, p.col_idx, decoded, p.B, threads=4)
+    assert (np.abs(got.cpu().numpy() - f64) <= 1e-4 * mag + 1e-6).all()
+    if kernel == "row":
+        assert np.array_equal(got.cpu().numpy(), want)
+    # odd nnz: the last byte holds one code only
+    q = G.random_csr(9, 12, 8, 0.0, seed=3, lengths=np.array([3, 0, 1, 2, 0, 0, 4, 0, 1]))
+    pk, sc = ops.e2m1_quantize(q.values)
+    g2 = ops.spmm(dev(q.row_ptr), dev(q.col_idx), pk.cuda(), dev(q.B), kernel=kernel, e2m1_scale=sc, nnz=q.nnz, sync=True)
+    w2 = oracle.spmm(q.row_ptr, q.col_idx, oracle.e2m1_decode(pk.numpy(), q.nnz, sc), q.B)
+    assert np.allclose(g2.cpu().numpy(), w2, rtol=RTOL, atol=ATOL)
+
+
+# ---- validation, statistics, error reporting -----------------------------------------------------------
+
+def test_validate_and_row_stats_on_device(cuda_lib):
+    p = G.make("cfg3_powerlaw", scale=64)
+    rp, ci = dev(p.row_ptr), dev(p.col_idx)
+    assert ops.validate_csr(rp, ci, p.Kd) == 0
+    st = ops.row_stats(rp)
+    lens = np.diff(p.row_ptr)
+    mean = p.nnz // p.M
+    assert st["max_row_nnz"] == lens.max() and st["empty_rows"] == (lens == 0).sum()
+    assert st["long_rows"] == (lens > 32 * (mean + 1)).sum()
+    assert st["long_rows_nnz"] == lens[lens > 32 * (mean + 1)].sum()
+    bad = p.col_idx.copy()
+    bad[5] = p.Kd
+    with pytest.raises(_lib.SpmmError) as e:
+        ops.validate_csr(rp, dev(bad), p.Kd)
+    assert e.value.status == _lib.ERR_INVALID_CSR
+    bad_rp = p.row_ptr.copy()
+    bad_rp[10], bad_rp[11] = bad_rp[11], bad_rp[10] - 1
+    with pytest.raises(_lib.SpmmError):
+        ops.validate_csr(dev(bad_rp), ci, p.Kd)
+
+
+@pytest.mark.parametrize("kernel", KERNELS)
+def test_out_of_range_column_is_clamped_and_reported(cuda_lib, kernel):
+    """A bad index must not become a bad address: the kernels clamp it and flag the status word."""
+    p = G.random_csr(40, 32, 16, 0.2, seed=51)
+    bad = p.col_idx.copy()
+    bad[7] = p.Kd  # one past the last row of B
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    with pytest.raises(_lib.SpmmError) as e:
+        ops.spmm(dev(p.row_ptr), dev(bad), dev(p.values), dev(p.B), kernel=kernel, status_word=status, sync=True)
+    assert e.value.status == _lib.ERR_INVALID_CSR and int(status.item()) & 2
+    # the context is still healthy
+    assert_parity(run(arrays(p), kernel), *arrays(p), exact=(kernel == "row"))
+
+
+def test_workspace_and_pin_errors(cuda_lib):
+    p = G.random_csr(300, 300, 66, 0.05, seed=61)
+    rp, ci, va, B = (dev(x) for x in arrays(p))
+    with pytest.raises(_lib.SpmmError) as e:
+        ops.spmm(rp, ci, va, B, kernel="tma")  # 66 columns: rows of B not 16-byte aligned
+    assert e.value.status == _lib.ERR_UNSUPPORTED
+    import ctypes as C
+    C_out = torch.empty(p.M, p.Nd, device="cuda")
+    small = torch.empty(256, dtype=torch.uint8, device="cuda")
+    a = _lib.make_args(p.M, p.Kd, p.Nd, p.nnz, rp.data_ptr(), ci.data_ptr(), va.data_ptr(), B.data_ptr(),
+                       C_out.data_ptr(), kernel=_lib.KERNEL_MERGE, workspace=small.data_ptr(), workspace_bytes=16)
+    assert cuda_lib.csrspmm_b200_spmm(C.byref(a), None) == _lib.ERR_WORKSPACE
+    # library-owned scratch (no workspace passed): stream-ordered allocation inside the call
+    a = _lib.make_args(p.M, p.Kd, p.Nd, p.nnz, rp.data_ptr(), ci.data_ptr(), va.data_ptr(), B.data_ptr(),
+                       C_out.data_ptr(), kernel=_lib.KERNEL_MERGE)
+    torch.cuda.synchronize()
+    assert cuda_lib.csrspmm_b200_spmm_sync(C.byref(a), None) == _lib.OK
+    assert np.allclose(C_out.cpu().numpy(), oracle.spmm(*arrays(p)), rtol=RTOL, atol=ATOL)
+
+
+def test_non_default_stream_and_host_round_trip(cuda_lib):
+    p = G.make("cfg2_medium")
+    want = oracle.spmm(*arrays(p), threads=4)
+    s = torch.cuda.Stream()
+    with torch.cuda.stream(s):
+        t = [dev(x) for x in arrays(p)]
+        out = ops.spmm(*t, kernel="merge")
+    s.synchronize()
+    assert np.allclose(out.cpu().numpy(), want, rtol=RTOL, atol=ATOL)
+    # host buffers in, host buffer out (csrspmm_b200_spmm_host), with and without a caller arena
+    h = [torch.from_numpy(x).pin_memory() for x in arrays(p)]
+    C_host = torch.empty(p.M, p.Nd).pin_memory()
+    ops.spmm_host(*h, C_host)
+    assert np.allclose(C_host.numpy(), want, rtol=RTOL, atol=ATOL)
+    arena = torch.empty(ops.host_arena_bytes(p.M, p.Kd, p.Nd, p.nnz), dtype=torch.uint8, device="cuda")
+    C_host.fill_(1.0)
+    ops.spmm_host(*h, C_host, 2.0, 0.5, arena=arena)
+    assert np.allclose(C_host.numpy(), 2.0 * want + 0.5, rtol=RTOL, atol=2e-6)
