@@ -45,7 +45,12 @@ FALLBACK_HBM_GBS = 6650.0
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu
 # captures summarised under profiles/ (bytes; None = not captured yet)
-NCU_TRAFFIC = {}
+NCU_TRAFFIC = {
+    ("cfg3_powerlaw", "merge"): 3.452e9,      # full-size capture, profiles/merge_kernel_cfg3_powerlaw.md
+    ("cfg5_xl", "merge"): 8.0 * 32.96e9,      # capture at 1/8 of the rows scaled by the non-zero count,
+                                              # profiles/merge_kernel_cfg5_xl_eighth.md
+    ("cfg2_medium", "row"): 10.6e6,           # profiles/row_kernel_cfg2_medium.md
+}
 
 
 def measured_peak():
