@@ -20,13 +20,14 @@ KERNEL_AUTO, KERNEL_ROW, KERNEL_MERGE, KERNEL_TMA = range(4)
 KERNEL_NAMES = {KERNEL_AUTO: "auto", KERNEL_ROW: "row", KERNEL_MERGE: "merge", KERNEL_TMA: "tma"}
 KERNEL_IDS = {v: k for k, v in KERNEL_NAMES.items()}
 VALUES_F32, VALUES_E2M1 = 0, 1
+NOALLOC_SCRATCH_BYTES = 8 << 20
 
 CSR_BAD_ROWPTR0, CSR_BAD_ROWPTR_END, CSR_NOT_MONOTONE, CSR_COL_RANGE, CSR_COL_UNSORTED = 1, 2, 4, 8, 16
 
 # every symbol include/csrspmm_b200.h declares
 EXPORTED_SYMBOLS = (
     "csrspmm_b200_abi_version", "csrspmm_b200_status_string", "csrspmm_b200_last_error",
-    "csrspmm_b200_spmm", "csrspmm_b200_spmm_sync", "csrspmm_b200_spmm_host",
+    "csrspmm_b200_spmm", "csrspmm_b200_spmm_sync", "csrspmm_b200_spmm_host", "csrspmm_b200_spmm_noalloc",
     "csrspmm_b200_host_arena_bytes", "csrspmm_b200_workspace_bytes", "csrspmm_b200_select_kernel",
     "csrspmm_b200_validate_csr_host", "csrspmm_b200_validate_csr_device",
     "csrspmm_b200_row_stats_device", "csrspmm_b200_partition_rows", "csrspmm_b200_e2m1_scale",
@@ -92,7 +93,7 @@ def lib() -> C.CDLL:
     L.csrspmm_b200_status_string.argtypes = [C.c_int]
     L.csrspmm_b200_status_string.restype = C.c_char_p
     L.csrspmm_b200_last_error.restype = C.c_char_p
-    for name in ("csrspmm_b200_spmm", "csrspmm_b200_spmm_sync"):
+    for name in ("csrspmm_b200_spmm", "csrspmm_b200_spmm_sync", "csrspmm_b200_spmm_noalloc"):
         fn = getattr(L, name)
         fn.argtypes = [C.POINTER(Args), C.c_void_p]
         fn.restype = C.c_int

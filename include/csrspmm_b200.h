@@ -122,6 +122,21 @@ int csrspmm_b200_spmm_host(const csrspmm_b200_args* args, void* device_arena,
                            size_t device_arena_bytes, csrspmm_b200_stream_t stream);
 size_t csrspmm_b200_host_arena_bytes(const csrspmm_b200_args* args);
 
+/* No counterpart in the reference.  The same product as csrspmm_b200_spmm for callers that cannot
+ * obtain device memory at call time -- a process whose memory manager already owns the whole GPU,
+ * a plug-in whose host forbids allocation calls, a loop that must never enter the allocator.  It
+ * always runs the merge-path kernel and keeps that kernel's scratch in a fixed array inside the
+ * library's device image (CSRSPMM_B200_NOALLOC_SCRATCH_BYTES per GPU, held until the process
+ * ends), so it calls no allocation routine at all.  args.kernel / workspace / workspace_bytes are
+ * ignored.  A problem whose scratch (an int32 and a row of Nd floats per 1024..2048 of M + nnz)
+ * does not fit is refused with ERR_WORKSPACE and nothing is launched.  Every call on a device
+ * shares the one array: the previous call's contents are harmless (every slot that is read is
+ * rewritten first by the same call), but two calls running on the GPU at the same time corrupt
+ * each other -- do not overlap them.  The first call on each device looks up the array's device
+ * address; make it before any stream capture on that device. */
+#define CSRSPMM_B200_NOALLOC_SCRATCH_BYTES (8u << 20)
+int csrspmm_b200_spmm_noalloc(const csrspmm_b200_args* args, csrspmm_b200_stream_t stream);
+
 /* Scratch the split kernels need for this problem (0 for the row kernel).  Depends only on
  * sizes, never on matrix contents. */
 size_t csrspmm_b200_workspace_bytes(const csrspmm_b200_args* args);
