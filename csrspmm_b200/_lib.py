@@ -8,8 +8,11 @@ from __future__ import annotations
 import ctypes as C
 from pathlib import Path
 
+import os
+
 PKG = Path(__file__).resolve().parent
-LIB_PATH = PKG / "lib" / "libcsrspmm_b200.so"
+# CSRSPMM_B200_LIBRARY points at another build of the same library (kernel tuning experiments)
+LIB_PATH = Path(os.environ.get("CSRSPMM_B200_LIBRARY") or PKG / "lib" / "libcsrspmm_b200.so")
 
 OK = 0
 ERR_BAD_ARG, ERR_INVALID_CSR, ERR_UNSUPPORTED, ERR_CUDA, ERR_DEVICE_WAIT, ERR_WORKSPACE, ERR_NO_DEVICE = range(1, 8)

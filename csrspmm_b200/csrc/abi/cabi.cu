@@ -30,24 +30,26 @@ namespace {
         }                                                                                   \
     } while (0)
 
-template <int VW, int NV>
-constexpr int unroll_for()
-{
-    return VW == 1 ? 8 : (NV == 1 ? 8 : 4);
-}
-
-template <int G, int NV, int VW, int FMT>
+template <int S, int VW, int FMT>
 void launch_row(const SpmmParams& p, const Plan& plan, cudaStream_t st)
 {
-    spmm_row_kernel<G, NV, VW, unroll_for<VW, NV>(), FMT>
-        <<<(unsigned)plan.grid, kRowThreads, 0, st>>>(p);
+    constexpr int G = kShapes[S].G, NV = kShapes[S].NV;
+    constexpr int U = VW == 1 ? 8 : row_unroll(NV);
+    if (VW == 4 && plan.full)
+        spmm_row_kernel<G, NV, VW, U, FMT, (VW == 4)><<<(unsigned)plan.grid, kRowThreads, 0, st>>>(p);
+    else
+        spmm_row_kernel<G, NV, VW, U, FMT, false><<<(unsigned)plan.grid, kRowThreads, 0, st>>>(p);
 }
 
-template <int G, int NV, int VW, int TG, int FMT>
+template <int S, int VW, int FMT>
 void launch_merge(const SpmmParams& p, const Plan& plan, cudaStream_t st)
 {
-    spmm_merge_kernel<G, NV, VW, TG, unroll_for<VW, NV>(), FMT>
-        <<<(unsigned)plan.grid, kMergeThreads, 0, st>>>(p);
+    constexpr int G = kShapes[S].G, NV = kShapes[S].NV, TG = kShapes[S].TG;
+    constexpr int U = VW == 1 ? 8 : merge_unroll(NV);
+    if (VW == 4 && plan.full)
+        spmm_merge_kernel<G, NV, VW, TG, U, FMT, (VW == 4)><<<(unsigned)plan.grid, kMergeThreads, 0, st>>>(p);
+    else
+        spmm_merge_kernel<G, NV, VW, TG, U, FMT, false><<<(unsigned)plan.grid, kMergeThreads, 0, st>>>(p);
 }
 
 template <int NV, int FMT>
@@ -66,11 +68,11 @@ template <int VW, int FMT>
 void dispatch_row(const SpmmParams& p, const Plan& plan, cudaStream_t st)
 {
     switch (plan.shape) {
-        case 0: launch_row<8, 1, VW, FMT>(p, plan, st); break;
-        case 1: launch_row<16, 1, VW, FMT>(p, plan, st); break;
-        case 2: launch_row<32, 1, VW, FMT>(p, plan, st); break;
-        case 3: launch_row<32, 2, VW, FMT>(p, plan, st); break;
-        default: launch_row<32, 4, VW, FMT>(p, plan, st); break;
+        case 0: launch_row<0, VW, FMT>(p, plan, st); break;
+        case 1: launch_row<1, VW, FMT>(p, plan, st); break;
+        case 2: launch_row<2, VW, FMT>(p, plan, st); break;
+        case 3: launch_row<3, VW, FMT>(p, plan, st); break;
+        default: launch_row<4, VW, FMT>(p, plan, st); break;
     }
 }
 
@@ -78,11 +80,11 @@ template <int VW, int FMT>
 void dispatch_merge(const SpmmParams& p, const Plan& plan, cudaStream_t st)
 {
     switch (plan.shape) {
-        case 0: launch_merge<8, 1, VW, kShapes[0].TG, FMT>(p, plan, st); break;
-        case 1: launch_merge<16, 1, VW, kShapes[1].TG, FMT>(p, plan, st); break;
-        case 2: launch_merge<32, 1, VW, kShapes[2].TG, FMT>(p, plan, st); break;
-        case 3: launch_merge<32, 2, VW, kShapes[3].TG, FMT>(p, plan, st); break;
-        default: launch_merge<32, 4, VW, kShapes[4].TG, FMT>(p, plan, st); break;
+        case 0: launch_merge<0, VW, FMT>(p, plan, st); break;
+        case 1: launch_merge<1, VW, FMT>(p, plan, st); break;
+        case 2: launch_merge<2, VW, FMT>(p, plan, st); break;
+        case 3: launch_merge<3, VW, FMT>(p, plan, st); break;
+        default: launch_merge<4, VW, FMT>(p, plan, st); break;
     }
 }
 
@@ -120,6 +122,7 @@ int enqueue(const csrspmm_b200_args* a, cudaStream_t st)
     p.value_scale = a->value_scale;
     p.B = a->B;
     p.ldb = a->ldb;
+    p.ldb_bytes = (unsigned)(a->ldb * 4);
     p.C = a->C;
     p.ldc = a->ldc;
     p.alpha = a->alpha;

@@ -74,16 +74,23 @@ int scratch_of_current_device(void** out)
     return CSRSPMM_B200_OK;
 }
 
+template <int S, int VW, int FMT>
+void launch_one(const SpmmParams& p, const Plan& plan, cudaStream_t st)
+{
+    constexpr int G = kShapes[S].G, NV = kShapes[S].NV, TG = kShapes[S].TG;
+    constexpr int U = VW == 1 ? 8 : merge_unroll(NV);
+    spmm_merge_kernel<G, NV, VW, TG, U, FMT, false><<<(unsigned)plan.grid, kMergeThreads, 0, st>>>(p);
+}
+
 template <int VW, int FMT>
 void launch_merge_for_shape(const SpmmParams& p, const Plan& plan, cudaStream_t st)
 {
-    const unsigned grid = (unsigned)plan.grid;
     switch (plan.shape) {
-        case 0: spmm_merge_kernel<8, 1, VW, kShapes[0].TG, 8, FMT><<<grid, kMergeThreads, 0, st>>>(p); break;
-        case 1: spmm_merge_kernel<16, 1, VW, kShapes[1].TG, 8, FMT><<<grid, kMergeThreads, 0, st>>>(p); break;
-        case 2: spmm_merge_kernel<32, 1, VW, kShapes[2].TG, 8, FMT><<<grid, kMergeThreads, 0, st>>>(p); break;
-        case 3: spmm_merge_kernel<32, 2, VW, kShapes[3].TG, (VW == 1 ? 8 : 4), FMT><<<grid, kMergeThreads, 0, st>>>(p); break;
-        default: spmm_merge_kernel<32, 4, VW, kShapes[4].TG, (VW == 1 ? 8 : 4), FMT><<<grid, kMergeThreads, 0, st>>>(p); break;
+        case 0: launch_one<0, VW, FMT>(p, plan, st); break;
+        case 1: launch_one<1, VW, FMT>(p, plan, st); break;
+        case 2: launch_one<2, VW, FMT>(p, plan, st); break;
+        case 3: launch_one<3, VW, FMT>(p, plan, st); break;
+        default: launch_one<4, VW, FMT>(p, plan, st); break;
     }
 }
 
@@ -126,6 +133,7 @@ extern "C" int csrspmm_b200_spmm_noalloc(const csrspmm_b200_args* args, csrspmm_
     p.value_scale = a.value_scale;
     p.B = a.B;
     p.ldb = a.ldb;
+    p.ldb_bytes = (unsigned)(a.ldb * 4);
     p.C = a.C;
     p.ldc = a.ldc;
     p.alpha = a.alpha;

@@ -44,6 +44,11 @@ int check_args(const csrspmm_b200_args* a, bool need_pointers)
         set_last_error("nnz > 0 with Kd == 0");
         return CSRSPMM_B200_ERR_BAD_ARG;
     }
+    if (a->ldb >= (1LL << 30) || a->ldc >= (1LL << 30)) {
+        set_last_error("leading dimension of 2^30 elements or more (ldb=%lld ldc=%lld)", (long long)a->ldb,
+                       (long long)a->ldc);
+        return CSRSPMM_B200_ERR_BAD_ARG;
+    }
     if (a->ldb < a->Nd || a->ldc < a->Nd) {
         set_last_error("leading dimension smaller than Nd (ldb=%lld ldc=%lld Nd=%d)",
                        (long long)a->ldb, (long long)a->ldc, a->Nd);
@@ -163,6 +168,7 @@ int make_plan(const csrspmm_b200_args* a, Plan* plan)
         plan->shape = shape_for(plan->ncolv);
         plan->G = kShapes[plan->shape].G;
         plan->NV = kShapes[plan->shape].NV;
+        plan->full = plan->VW == 4 && plan->G * plan->NV == plan->ncolv;
         if (kernel == CSRSPMM_B200_KERNEL_MERGE) {
             fill_split_geometry(a, plan, (256 / plan->G) * kShapes[plan->shape].TG);
         } else {
@@ -180,9 +186,14 @@ int make_plan(const csrspmm_b200_args* a, Plan* plan)
 size_t worst_case_workspace(const csrspmm_b200_args* a)
 {
     if (check_args(a, false) != CSRSPMM_B200_OK) return 0;
-    // the smallest tile any split kernel uses is 1024 items
+    // sized for the smallest tile any split kernel uses (most CTAs, most carry rows)
+    int tile = 8 * 128;  // TMA kernel
+    for (int k = 0; k < kNumShapes; ++k) {
+        const int t = (256 / kShapes[k].G) * kShapes[k].TG;
+        if (t < tile) tile = t;
+    }
     Plan p;
-    fill_split_geometry(a, &p, 1024);
+    fill_split_geometry(a, &p, tile);
     return p.workspace_bytes;
 }
 

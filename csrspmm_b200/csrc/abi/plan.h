@@ -8,13 +8,15 @@
 #include <cstddef>
 #include <cstdint>
 
+#include "../kernels/tuning.h"
 #include "csrspmm_b200.h"
 
 namespace csrspmm_b200 {
 
 struct Plan {
     int kernel = CSRSPMM_B200_KERNEL_ROW;  // resolved, never AUTO
-    int shape = 0;                         // index into kShapes
+    int shape = 0;                         // index into kShapes (tuning.h)
+    bool full = false;                     // one pass covers the row exactly: G*NV == ncolv
     int G = 8, NV = 1, VW = 4;             // lanes per group, vectors per lane, vector width
     int ncolv = 0;                         // ceil(Nd / VW)
     int tile = 0;                          // merge-path items per CTA (split kernels)
@@ -26,13 +28,6 @@ struct Plan {
     size_t workspace_bytes = 0;            // carry_row_bytes + carry values
     size_t dynamic_smem = 0;               // TMA kernel only
 };
-
-struct ShapeDesc {
-    int G, NV, TG;  // TG = merge-path items per lane group
-};
-constexpr int kNumShapes = 5;
-constexpr ShapeDesc kShapes[kNumShapes] = {
-    {8, 1, 64}, {16, 1, 128}, {32, 1, 128}, {32, 2, 128}, {32, 4, 128}};
 
 // Checks the argument block (sizes, enums, pointers) without touching memory.
 int check_args(const csrspmm_b200_args* a, bool need_pointers);

@@ -10,6 +10,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "tuning.h"
+
 namespace csrspmm_b200 {
 
 // Bits OR-ed into the optional device status word.
@@ -33,6 +35,7 @@ struct SpmmParams {
     float value_scale;
     const float* B;
     long long ldb;
+    unsigned ldb_bytes;  // ldb * 4 (< 2^32, checked on the host): one wide multiply per B-row address
     float* C;
     long long ldc;
     float alpha;
@@ -72,6 +75,24 @@ __device__ __forceinline__ float load_value(const void* values, int j, float sca
     }
 }
 
+// ---- L2 residency policy for the gathered operand -------------------------------------------------
+// B is the only operand that is re-read (once per non-zero that names the row); A streams through
+// once and C is written once.  When B is larger than L2 its lines compete with that streaming
+// traffic; B loads can carry an evict_last policy and C stores can be streaming stores
+// (compile-time options in tuning.h, off by default: they did not pay on B200).
+__device__ __forceinline__ unsigned long long make_b_policy()
+{
+    unsigned long long pol = 0;
+#if CSRSPMM_TUNE_B_EVICT_LAST_PCT >= 100
+    asm("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(pol));
+#elif CSRSPMM_TUNE_B_EVICT_LAST_PCT > 0
+    asm("createpolicy.fractional.L2::evict_last.L2::evict_first.b64 %0, %1;"
+        : "=l"(pol)
+        : "f"(CSRSPMM_TUNE_B_EVICT_LAST_PCT / 100.0f));
+#endif
+    return pol;
+}
+
 // ---- column vectors (VW = 4: float4, 16-byte aligned; VW = 1: one float) --------------------------
 
 template <int VW>
@@ -82,6 +103,17 @@ struct Vec<4> {
     float4 v;
     __device__ __forceinline__ void zero() { v = make_float4(0.f, 0.f, 0.f, 0.f); }
     __device__ __forceinline__ void load_nc(const float* p) { v = __ldg(reinterpret_cast<const float4*>(p)); }
+    __device__ __forceinline__ void load_b(const float* p, unsigned long long pol)
+    {
+#if CSRSPMM_TUNE_B_EVICT_LAST_PCT > 0
+        asm("ld.global.nc.L2::cache_hint.v4.f32 {%0, %1, %2, %3}, [%4], %5;"
+            : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+            : "l"(p), "l"(pol));
+#else
+        (void)pol;
+        load_nc(p);
+#endif
+    }
     __device__ __forceinline__ void load(const float* p) { v = *reinterpret_cast<const float4*>(p); }
     __device__ __forceinline__ void store(float* p) const { *reinterpret_cast<float4*>(p) = v; }
     __device__ __forceinline__ void store_streaming(float* p) const { __stcs(reinterpret_cast<float4*>(p), v); }
@@ -135,6 +167,15 @@ struct Vec<1> {
     float v;
     __device__ __forceinline__ void zero() { v = 0.f; }
     __device__ __forceinline__ void load_nc(const float* p) { v = __ldg(p); }
+    __device__ __forceinline__ void load_b(const float* p, unsigned long long pol)
+    {
+#if CSRSPMM_TUNE_B_EVICT_LAST_PCT > 0
+        asm("ld.global.nc.L2::cache_hint.f32 %0, [%1], %2;" : "=f"(v) : "l"(p), "l"(pol));
+#else
+        (void)pol;
+        load_nc(p);
+#endif
+    }
     __device__ __forceinline__ void load(const float* p) { v = *p; }
     __device__ __forceinline__ void store(float* p) const { *p = v; }
     __device__ __forceinline__ void store_streaming(float* p) const { __stcs(p, v); }
@@ -171,6 +212,15 @@ __device__ __forceinline__ void store_row(const SpmmParams& p, int row, int cb, 
         const int cv = cb + lane + v * G;
         if (cv < p.ncolv) {
             float* cp = crow + (long long)cv * VW;
+#if CSRSPMM_TUNE_C_STREAMING
+            if (p.beta != 0.0f) {
+                Vec<VW> old;
+                old.load(cp);
+                acc[v].epilogue(p.alpha, p.beta, old).store_streaming(cp);
+            } else {
+                acc[v].epilogue0(p.alpha).store_streaming(cp);
+            }
+#else
             if (p.beta != 0.0f) {
                 Vec<VW> old;
                 old.load(cp);
@@ -178,6 +228,7 @@ __device__ __forceinline__ void store_row(const SpmmParams& p, int row, int cb, 
             } else {
                 acc[v].epilogue0(p.alpha).store(cp);
             }
+#endif
         }
     }
 }

@@ -28,6 +28,7 @@
 #include <limits.h>
 
 #include "common.cuh"
+#include "tuning.h"
 
 namespace csrspmm_b200 {
 
@@ -78,8 +79,7 @@ struct MergeSmem {
     static constexpr int TILE = GROUPS * TG;
     static constexpr int ROWW = G * NV * VW;  // floats one group holds per pass
     int rowend[TILE + 1];
-    int col[TILE];
-    float val[TILE];
+    alignas(8) int2 cv[TILE];  // (column index, value bits) of each staged non-zero
     int coord[4];
     int tail_row[GROUPS];
     alignas(16) float tail[GROUPS][ROWW];
@@ -136,8 +136,7 @@ __device__ __forceinline__ bool merge_tile_setup(const SpmmParams& p, Smem& s, T
             c = min(max(c, 0), p.Kd - 1);
             report_status(p, kStatusColClamped);
         }
-        s.col[k] = c;
-        s.val[k] = load_value<FMT>(p.values, r.j0 + k, p.value_scale);
+        s.cv[k] = make_int2(c, __float_as_int(load_value<FMT>(p.values, r.j0 + k, p.value_scale)));
     }
     __syncthreads();
 
@@ -219,8 +218,9 @@ __device__ __forceinline__ void merge_tile_finish(const SpmmParams& p, Smem& s, 
     }
 }
 
-template <int G, int NV, int VW, int TG, int U, int FMT>
-__global__ void __launch_bounds__(kMergeThreads, (NV >= 4 ? 2 : 3)) spmm_merge_kernel(const SpmmParams p)
+// FULL: one pass covers the row exactly (G * NV == ncolv), so no column guard is compiled in.
+template <int G, int NV, int VW, int TG, int U, int FMT, bool FULL>
+__global__ void __launch_bounds__(kMergeThreads, merge_min_blocks(NV)) spmm_merge_kernel(const SpmmParams p)
 {
     using Smem = MergeSmem<G, NV, VW, TG>;
     __shared__ Smem s;
@@ -229,8 +229,15 @@ __global__ void __launch_bounds__(kMergeThreads, (NV >= 4 ? 2 : 3)) spmm_merge_k
     if (!merge_tile_setup<Smem, G, TG, FMT>(p, s, r)) return;
     const int g = threadIdx.x / G;
     const int lane = threadIdx.x % G;
+    const char* const b_lane = reinterpret_cast<const char*>(p.B) + (size_t)lane * (VW * 4);
+    const unsigned long long b_policy = make_b_policy();
 
     for (int cb = 0; cb < p.ncolv; cb += G * NV) {
+        const char* const b_pass = b_lane + (size_t)cb * (VW * 4);
+        bool col_ok[NV];
+#pragma unroll
+        for (int v = 0; v < NV; ++v) col_ok[v] = FULL || (cb + lane + v * G < p.ncolv);
+
         Vec<VW> acc[NV];
         Vec<VW> head[NV];  // the first row this group finishes is held back until step 4
 #pragma unroll
@@ -239,6 +246,7 @@ __global__ void __launch_bounds__(kMergeThreads, (NV >= 4 ? 2 : 3)) spmm_merge_k
             head[v].zero();
         }
         int i = r.il0;
+        int next_end = s.rowend[i];  // local position where row i ends (INT_MAX past the tile's rows)
         bool dirty = false;
 
         auto finish_row = [&]() {
@@ -252,29 +260,65 @@ __global__ void __launch_bounds__(kMergeThreads, (NV >= 4 ? 2 : 3)) spmm_merge_k
             for (int v = 0; v < NV; ++v) acc[v].zero();
             dirty = false;
             ++i;
+            next_end = s.rowend[i];
         };
 
-        for (int base = r.jl0; base < r.jl1; base += U) {
+        // B row of staged non-zero e: one 32x32->64 multiply-add gives the address
+        auto load_b = [&](Vec<VW> (&dst)[NV], int col) {
+            const char* brow = b_pass + (unsigned long long)(unsigned)col * p.ldb_bytes;
+#pragma unroll
+            for (int v = 0; v < NV; ++v) {
+                if (col_ok[v]) dst[v].load_b(reinterpret_cast<const float*>(brow + v * (G * VW * 4)), b_policy);
+                else dst[v].zero();
+            }
+        };
+
+        int base = r.jl0;
+        // whole batches of U non-zeros: loads first (they do not depend on the row structure),
+        // then the multiply-adds, without any per-element test when no row ends inside the batch
+        for (; base + U <= r.jl1; base += U) {
+            int2 e[U];
+            Vec<VW> bq[U][NV];
+#pragma unroll
+            for (int u = 0; u < U; ++u) e[u] = s.cv[base + u];
+#pragma unroll
+            for (int u = 0; u < U; ++u) load_b(bq[u], e[u].x);
+            if (base + U <= next_end) {
+#pragma unroll
+                for (int u = 0; u < U; ++u) {
+                    const float a = __int_as_float(e[u].y);
+#pragma unroll
+                    for (int v = 0; v < NV; ++v) acc[v].fma(a, bq[u][v]);
+                }
+                dirty = true;
+            } else {
+#pragma unroll
+                for (int u = 0; u < U; ++u) {
+                    while (base + u >= next_end) finish_row();  // rowend[nrows] = INT_MAX stops it
+                    const float a = __int_as_float(e[u].y);
+#pragma unroll
+                    for (int v = 0; v < NV; ++v) acc[v].fma(a, bq[u][v]);
+                    dirty = true;
+                }
+            }
+        }
+        // the last, partial batch
+        if (base < r.jl1) {
+            const int n = r.jl1 - base;
+            int2 e[U];
             Vec<VW> bq[U][NV];
 #pragma unroll
             for (int u = 0; u < U; ++u) {
-                const int jj = base + u;
-                if (jj < r.jl1) {
-                    const float* brow = p.B + (long long)s.col[jj] * p.ldb;
-#pragma unroll
-                    for (int v = 0; v < NV; ++v) {
-                        const int cv = cb + lane + v * G;
-                        if (cv < p.ncolv) bq[u][v].load_nc(brow + (long long)cv * VW);
-                        else bq[u][v].zero();
-                    }
+                if (u < n) {
+                    e[u] = s.cv[base + u];
+                    load_b(bq[u], e[u].x);
                 }
             }
 #pragma unroll
             for (int u = 0; u < U; ++u) {
-                const int jj = base + u;
-                if (jj < r.jl1) {
-                    while (jj >= s.rowend[i]) finish_row();  // rowend[nrows] = INT_MAX stops it
-                    const float a = s.val[jj];
+                if (u < n) {
+                    while (base + u >= next_end) finish_row();
+                    const float a = __int_as_float(e[u].y);
 #pragma unroll
                     for (int v = 0; v < NV; ++v) acc[v].fma(a, bq[u][v]);
                     dirty = true;

@@ -13,6 +13,7 @@
 #include <cooperative_groups.h>
 
 #include "common.cuh"
+#include "tuning.h"
 
 namespace csrspmm_b200 {
 
@@ -20,8 +21,9 @@ namespace cg = cooperative_groups;
 
 constexpr int kRowThreads = 256;
 
-template <int G, int NV, int VW, int U, int FMT>
-__global__ void __launch_bounds__(kRowThreads) spmm_row_kernel(const SpmmParams p)
+// FULL: one pass covers the row exactly (G * NV == ncolv), so no column guard is compiled in.
+template <int G, int NV, int VW, int U, int FMT, bool FULL>
+__global__ void __launch_bounds__(kRowThreads, CSRSPMM_TUNE_ROW_MINB) spmm_row_kernel(const SpmmParams p)
 {
     constexpr int GROUPS = kRowThreads / G;
     const cg::thread_block_tile<G> tile = cg::tiled_partition<G>(cg::this_thread_block());
@@ -33,11 +35,26 @@ __global__ void __launch_bounds__(kRowThreads) spmm_row_kernel(const SpmmParams 
     // clamped so that a malformed row_ptr cannot index outside col_idx/values
     const int rs = max(__ldg(p.row_ptr + row), 0);
     const int re = min(__ldg(p.row_ptr + row + 1), p.nnz);
+    const char* const b_lane = reinterpret_cast<const char*>(p.B) + (size_t)lane * (VW * 4);
+    const unsigned long long b_policy = make_b_policy();
 
     for (int cb = 0; cb < p.ncolv; cb += G * NV) {
+        const char* const b_pass = b_lane + (size_t)cb * (VW * 4);
+        bool col_ok[NV];
+#pragma unroll
+        for (int v = 0; v < NV; ++v) col_ok[v] = FULL || (cb + lane + v * G < p.ncolv);
         Vec<VW> acc[NV];
 #pragma unroll
         for (int v = 0; v < NV; ++v) acc[v].zero();
+
+        auto load_b = [&](Vec<VW> (&dst)[NV], int col) {
+            const char* brow = b_pass + (unsigned long long)(unsigned)col * p.ldb_bytes;
+#pragma unroll
+            for (int v = 0; v < NV; ++v) {
+                if (col_ok[v]) dst[v].load_b(reinterpret_cast<const float*>(brow + v * (G * VW * 4)), b_policy);
+                else dst[v].zero();
+            }
+        };
 
         for (int base = rs; base < re; base += G) {
             const int jj = base + lane;
@@ -52,21 +69,23 @@ __global__ void __launch_bounds__(kRowThreads) spmm_row_kernel(const SpmmParams 
                 }
             }
             const int n = min(G, re - base);
-            for (int t = 0; t < n; t += U) {
+            int t = 0;
+            for (; t + U <= n; t += U) {  // whole batches: no per-element test
                 Vec<VW> bq[U][NV];
 #pragma unroll
-                for (int u = 0; u < U; ++u) {
-                    if (t + u < n) {
-                        const int c = tile.shfl(c_l, t + u);
-                        const float* brow = p.B + (long long)c * p.ldb;
+                for (int u = 0; u < U; ++u) load_b(bq[u], tile.shfl(c_l, t + u));
 #pragma unroll
-                        for (int v = 0; v < NV; ++v) {
-                            const int cv = cb + lane + v * G;
-                            if (cv < p.ncolv) bq[u][v].load_nc(brow + (long long)cv * VW);
-                            else bq[u][v].zero();
-                        }
-                    }
+                for (int u = 0; u < U; ++u) {
+                    const float a = tile.shfl(a_l, t + u);
+#pragma unroll
+                    for (int v = 0; v < NV; ++v) acc[v].fma(a, bq[u][v]);
                 }
+            }
+            if (t < n) {  // the last, partial batch
+                Vec<VW> bq[U][NV];
+#pragma unroll
+                for (int u = 0; u < U; ++u)
+                    if (t + u < n) load_b(bq[u], tile.shfl(c_l, t + u));
 #pragma unroll
                 for (int u = 0; u < U; ++u) {
                     if (t + u < n) {

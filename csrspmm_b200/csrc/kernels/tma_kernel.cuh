@@ -88,8 +88,7 @@ struct TmaSmem {
     static constexpr int TILE = GROUPS * TG;
     static constexpr int ROWW = 32 * NV * 4;
     int rowend[TILE + 1];
-    int col[TILE];
-    float val[TILE];
+    alignas(8) int2 cv[TILE];  // (column index, value bits) of each staged non-zero
     int coord[4];
     int tail_row[GROUPS];
     alignas(16) float tail[GROUPS][ROWW];
@@ -153,7 +152,7 @@ __global__ void __launch_bounds__(kMergeThreads) spmm_tma_kernel(const SpmmParam
         for (int k = 0; k < min(SLOTS, n); ++k) {
             const unsigned bar = bar_base + k * 8u;
             mbar_expect_tx(bar, row_bytes);
-            bulk_copy_g2s(ring_base + k * slot_bytes, p.B + (long long)s.col[r.jl0 + k] * p.ldb, row_bytes, bar);
+            bulk_copy_g2s(ring_base + k * slot_bytes, p.B + (long long)s.cv[r.jl0 + k].x * p.ldb, row_bytes, bar);
         }
     }
     issued = min(SLOTS, n);
@@ -169,7 +168,7 @@ __global__ void __launch_bounds__(kMergeThreads) spmm_tma_kernel(const SpmmParam
         }
         const int jj = r.jl0 + k;
         while (jj >= s.rowend[i]) finish_row();
-        const float a = s.val[jj];
+        const float a = __int_as_float(s.cv[jj].y);
         const float* srow = reinterpret_cast<const float*>(my_ring + (size_t)slot * slot_bytes);
 #pragma unroll
         for (int v = 0; v < NV; ++v) {
@@ -188,7 +187,7 @@ __global__ void __launch_bounds__(kMergeThreads) spmm_tma_kernel(const SpmmParam
                 const unsigned bar = bar_base + slot * 8u;
                 mbar_expect_tx(bar, row_bytes);
                 bulk_copy_g2s(ring_base + slot * slot_bytes,
-                              p.B + (long long)s.col[r.jl0 + k + SLOTS] * p.ldb, row_bytes, bar);
+                              p.B + (long long)s.cv[r.jl0 + k + SLOTS].x * p.ldb, row_bytes, bar);
             }
             ++issued;
         }

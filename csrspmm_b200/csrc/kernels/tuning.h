@@ -1,0 +1,114 @@
+// Compile-time tuning constants of the SpMM kernels.  Every value can be overridden on the
+// compiler command line (-DCSRSPMM_TUNE_...=n) to build an experimental variant of the library;
+// the defaults are the measured best on B200.
+#pragma once
+
+// B-row loads kept in flight per lane, by number of column vectors per lane (NV) -- merge kernel
+#ifndef CSRSPMM_TUNE_MERGE_U_NV1
+#define CSRSPMM_TUNE_MERGE_U_NV1 6
+#endif
+#ifndef CSRSPMM_TUNE_MERGE_U_NV2
+#define CSRSPMM_TUNE_MERGE_U_NV2 4
+#endif
+#ifndef CSRSPMM_TUNE_MERGE_U_NV4
+#define CSRSPMM_TUNE_MERGE_U_NV4 3
+#endif
+// ... and row kernel
+#ifndef CSRSPMM_TUNE_ROW_U_NV1
+#define CSRSPMM_TUNE_ROW_U_NV1 4
+#endif
+#ifndef CSRSPMM_TUNE_ROW_U_NV2
+#define CSRSPMM_TUNE_ROW_U_NV2 4
+#endif
+#ifndef CSRSPMM_TUNE_ROW_U_NV4
+#define CSRSPMM_TUNE_ROW_U_NV4 4
+#endif
+
+// L2 residency hints: rows of B loaded with an evict_last policy applied to this percentage of
+// the lines, C written with streaming stores.  Both are OFF by default: on B200 neither helped
+// (config 3, B = 2.1 x L2: 685 us without hints, 687-714 us with any combination of them).
+#ifndef CSRSPMM_TUNE_B_EVICT_LAST_PCT
+#define CSRSPMM_TUNE_B_EVICT_LAST_PCT 0
+#endif
+#ifndef CSRSPMM_TUNE_C_STREAMING
+#define CSRSPMM_TUNE_C_STREAMING 0
+#endif
+
+// minimum resident CTAs per SM requested from the compiler (caps registers per thread)
+#ifndef CSRSPMM_TUNE_MERGE_MINB_NV1
+#define CSRSPMM_TUNE_MERGE_MINB_NV1 4
+#endif
+#ifndef CSRSPMM_TUNE_MERGE_MINB_NV2
+#define CSRSPMM_TUNE_MERGE_MINB_NV2 3
+#endif
+#ifndef CSRSPMM_TUNE_MERGE_MINB_NV4
+#define CSRSPMM_TUNE_MERGE_MINB_NV4 2
+#endif
+#ifndef CSRSPMM_TUNE_ROW_MINB
+#define CSRSPMM_TUNE_ROW_MINB 1
+#endif
+
+// lane-group shapes by dense width class k (column vectors per row <= 8, 16, 32, 64, more):
+// lanes per group G, vectors per lane NV, merge-path items per group TG
+#ifndef CSRSPMM_TUNE_S0_G
+#define CSRSPMM_TUNE_S0_G 8
+#endif
+#ifndef CSRSPMM_TUNE_S0_NV
+#define CSRSPMM_TUNE_S0_NV 1
+#endif
+#ifndef CSRSPMM_TUNE_S0_TG
+#define CSRSPMM_TUNE_S0_TG 64
+#endif
+#ifndef CSRSPMM_TUNE_S1_G
+#define CSRSPMM_TUNE_S1_G 16
+#endif
+#ifndef CSRSPMM_TUNE_S1_NV
+#define CSRSPMM_TUNE_S1_NV 1
+#endif
+#ifndef CSRSPMM_TUNE_S1_TG
+#define CSRSPMM_TUNE_S1_TG 128
+#endif
+#ifndef CSRSPMM_TUNE_S2_G
+#define CSRSPMM_TUNE_S2_G 32
+#endif
+#ifndef CSRSPMM_TUNE_S2_NV
+#define CSRSPMM_TUNE_S2_NV 1
+#endif
+#ifndef CSRSPMM_TUNE_S2_TG
+#define CSRSPMM_TUNE_S2_TG 128
+#endif
+#ifndef CSRSPMM_TUNE_S3_G
+#define CSRSPMM_TUNE_S3_G 32
+#endif
+#ifndef CSRSPMM_TUNE_S3_NV
+#define CSRSPMM_TUNE_S3_NV 2
+#endif
+#ifndef CSRSPMM_TUNE_S3_TG
+#define CSRSPMM_TUNE_S3_TG 128
+#endif
+#ifndef CSRSPMM_TUNE_S4_G
+#define CSRSPMM_TUNE_S4_G 32
+#endif
+#ifndef CSRSPMM_TUNE_S4_NV
+#define CSRSPMM_TUNE_S4_NV 4
+#endif
+#ifndef CSRSPMM_TUNE_S4_TG
+#define CSRSPMM_TUNE_S4_TG 128
+#endif
+
+namespace csrspmm_b200 {
+
+struct ShapeDesc {
+    int G, NV, TG;
+};
+constexpr int kNumShapes = 5;
+constexpr ShapeDesc kShapes[kNumShapes] = {
+    {CSRSPMM_TUNE_S0_G, CSRSPMM_TUNE_S0_NV, CSRSPMM_TUNE_S0_TG}, {CSRSPMM_TUNE_S1_G, CSRSPMM_TUNE_S1_NV, CSRSPMM_TUNE_S1_TG},
+    {CSRSPMM_TUNE_S2_G, CSRSPMM_TUNE_S2_NV, CSRSPMM_TUNE_S2_TG}, {CSRSPMM_TUNE_S3_G, CSRSPMM_TUNE_S3_NV, CSRSPMM_TUNE_S3_TG},
+    {CSRSPMM_TUNE_S4_G, CSRSPMM_TUNE_S4_NV, CSRSPMM_TUNE_S4_TG}};
+
+constexpr int merge_unroll(int nv) { return nv == 1 ? CSRSPMM_TUNE_MERGE_U_NV1 : (nv == 2 ? CSRSPMM_TUNE_MERGE_U_NV2 : CSRSPMM_TUNE_MERGE_U_NV4); }
+constexpr int row_unroll(int nv) { return nv == 1 ? CSRSPMM_TUNE_ROW_U_NV1 : (nv == 2 ? CSRSPMM_TUNE_ROW_U_NV2 : CSRSPMM_TUNE_ROW_U_NV4); }
+constexpr int merge_min_blocks(int nv) { return nv == 1 ? CSRSPMM_TUNE_MERGE_MINB_NV1 : (nv == 2 ? CSRSPMM_TUNE_MERGE_MINB_NV2 : CSRSPMM_TUNE_MERGE_MINB_NV4); }
+
+}  // namespace csrspmm_b200
