@@ -46,11 +46,22 @@ FALLBACK_HBM_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu
 # captures summarised under profiles/ (bytes; None = not captured yet)
 NCU_TRAFFIC = {
-    ("cfg3_powerlaw", "merge"): 3.452e9,      # full-size capture, profiles/merge_kernel_cfg3_powerlaw.md
-    ("cfg5_xl", "merge"): 8.0 * 32.96e9,      # capture at 1/8 of the rows scaled by the non-zero count,
-                                              # profiles/merge_kernel_cfg5_xl_eighth.md
-    ("cfg2_medium", "row"): 10.6e6,           # profiles/row_kernel_cfg2_medium.md
+    # (workload, kernel): (bytes per launch in the capture, non-zeros of the captured case)
+    ("cfg3_powerlaw", "merge"): (3.888e9, 16802627),   # full size, profiles/merge_kernel_cfg3_powerlaw.md
+    ("cfg5_xl", "tma"): (32.88e9, 16777248),           # 1/8 of the rows, profiles/tma_and_merge_kernel_cfg5_xl_eighth.md
+    ("cfg5_xl", "merge"): (32.96e9, 16777248),         # 1/8 of the rows, same file
+    ("cfg2_medium", "row"): (10.6e6, 268783),          # profiles/row_kernel_cfg2_medium_and_cfg4.md
+    ("cfg4_fp4", "row"): (1.412e9, 21471764),          # same file
 }
+
+
+def ncu_traffic(workload, kernel, nnz):
+    """DRAM bytes per launch from the committed ncu capture, scaled by the non-zero count when the
+    captured case was smaller than (or a different shard of) what is being timed."""
+    ent = NCU_TRAFFIC.get((workload.split("/")[0], kernel))
+    if ent is None:
+        return None
+    return ent[0] * (nnz / ent[1])
 
 
 def measured_peak():
@@ -184,6 +195,47 @@ def cusparse_via_torch(torch, t, M, Kd, steps, warmup, flush_buf):
         return sum(s.elapsed_time(e) for s, e in zip(starts, stops)) / 1e3 / steps
     except Exception as e:  # comparator is best effort
         return f"unavailable: {type(e).__name__}: {e}"[:200]
+
+
+def cusparse_direct(torch, t, M, Kd, Nd, nnz, C_out, steps, warmup, flush_buf):
+    """cusparseSpMM through the comparator library (csrc/cmp/cusparse_cmp.cu): every CSR algorithm,
+    with and without cusparseSpMM_preprocess.  Returns {name: seconds} or a reason string."""
+    import ctypes as C
+    lib_path = ROOT / "csrspmm_b200" / "lib" / "libcsrspmm_b200_cusparse_cmp.so"
+    if not lib_path.exists():
+        return "unavailable: comparator library not built"
+    try:
+        L = C.CDLL(str(lib_path))
+        fn = L.csrspmm_cmp_cusparse_spmm
+        fn.argtypes = [C.c_int, C.c_int, C.c_int, C.c_longlong, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                       C.c_void_p, C.c_float, C.c_float, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_size_t,
+                       C.c_void_p, C.POINTER(C.c_double), C.POINTER(C.c_size_t)]
+        fn.restype = C.c_int
+        out = {}
+        stream = torch.cuda.current_stream().cuda_stream
+        for alg, name in ((0, "default"), (1, "csr_alg1"), (2, "csr_alg2"), (3, "csr_alg3")):
+            for pre in (0, 1):
+                sec, buf = C.c_double(0.0), C.c_size_t(0)
+                rc = fn(M, Kd, Nd, nnz, t["row_ptr"].data_ptr(), t["col_idx"].data_ptr(), t["values"].data_ptr(),
+                        t["B"].data_ptr(), C_out.data_ptr(), 1.0, 0.0, alg, pre, warmup, steps,
+                        flush_buf.data_ptr() if flush_buf is not None else None,
+                        flush_buf.numel() if flush_buf is not None else 0, C.c_void_p(stream), C.byref(sec), C.byref(buf))
+                torch.cuda.synchronize()
+                out[name + ("+preprocess" if pre else "")] = sec.value if rc == 0 else f"error {rc}"
+        return out
+    except Exception as e:
+        return f"unavailable: {type(e).__name__}: {e}"[:200]
+
+
+def cusparse_summary(res, flops):
+    if not isinstance(res, dict):
+        return res
+    ok = {k: v for k, v in res.items() if isinstance(v, float) and v > 0}
+    if not ok:
+        return res
+    best = min(ok, key=ok.get)
+    return {"best": best, "gflops": flops / ok[best] / 1e9, "us": ok[best] * 1e6,
+            "all_us": {k: (round(v * 1e6, 1) if isinstance(v, float) else v) for k, v in res.items()}}
 
 
 def cpu_sample(torch, G, oracle, prob, sample_rows, threads, repeats=2):
@@ -414,7 +466,7 @@ def main(argv=None):
                    "broadcast_s": round(t_bcast, 3)},
         "gpu_launches": ns.steps * launches_per_step,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "traffic": NCU_TRAFFIC.get((prob.name, chosen)), "peak_kind": f"of {peak_kind}",
+                     "traffic": ncu_traffic(prob.name, chosen, my_nnz), "peak_kind": f"of {peak_kind}",
                      "algorithmic_bytes": my_bytes, "b_rows_touched": touched,
                      "gather_bytes": gather_bytes, "gather_GBps": gather_bytes / sec / 1e9,
                      "scope": "rank 0's row block, main kernel + fix-up kernel"},
@@ -432,6 +484,8 @@ def main(argv=None):
         line["cpu_baseline"] = {"value": g, "unit": "GFLOPS", "cores": oracle.max_threads(), "kind": "port",
                                 "sample": f"rows [0, {rows}) of {M} ({n_s} of {nnz} nnz), B complete on the host, "
                                           f"best of 2, {best:.2f} s"}
+        line["cusparse"] = cusparse_summary(
+            cusparse_direct(torch, t, my_rows, Kd, Nd, my_nnz, C_out, min(ns.steps, 5), 2, flush_buf), flops_total)
         del prob, t, B, C_out, workspace, shard
         torch.cuda.empty_cache()
         line["other_workloads"] = other_workloads(torch, ops, G, ns, dev, peak)
@@ -467,6 +521,7 @@ def other_workloads(torch, ops, G, ns, dev, peak):
             entry["auto"] = auto
             cs = cusparse_via_torch(torch, t, p.M, p.Kd, 20, 3, fb)
             entry["cusparse_torch"] = {"gflops": flops / cs / 1e9, "us": cs * 1e6} if isinstance(cs, float) else cs
+            entry["cusparse"] = cusparse_summary(cusparse_direct(torch, t, p.M, p.Kd, p.Nd, p.nnz, C_out, 20, 3, fb), flops)
             if name == "cfg4_fp4":
                 packed, scale = ops.e2m1_quantize(p.values)
                 e = (packed.to(dev), scale, p.nnz)

@@ -36,8 +36,26 @@ def nvcc() -> str:
     return cand
 
 
+CMP_SRC = CSRC / "cmp" / "cusparse_cmp.cu"
+CMP_LIB = LIB_DIR / "libcsrspmm_b200_cusparse_cmp.so"
+
+
 def sources() -> list[Path]:
-    return sorted(list(CSRC.rglob("*.cu")) + list(CSRC.rglob("*.cpp")))
+    """Sources of the SpMM library itself (the cuSPARSE comparator under cmp/ is a separate object)."""
+    return sorted(p for p in list(CSRC.rglob("*.cu")) + list(CSRC.rglob("*.cpp")) if p.parent.name != "cmp")
+
+
+def build_comparator() -> Path:
+    """libcsrspmm_b200_cusparse_cmp.so: cusparseSpMM timed on the bench's buffers (bench.py only)."""
+    LIB_DIR.mkdir(exist_ok=True)
+    if CMP_LIB.exists() and CMP_LIB.stat().st_mtime >= CMP_SRC.stat().st_mtime:
+        return CMP_LIB
+    cmd = [nvcc(), *ARCH_FLAGS, "-O2", "-std=c++17", "-shared", "-Xcompiler", "-fPIC", "-ccbin",
+           shutil.which("g++") or "g++", "-o", str(CMP_LIB), str(CMP_SRC), "-lcusparse"]
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if res.returncode != 0:
+        raise RuntimeError(f"nvcc failed for {CMP_SRC}:\n{res.stdout}\n{res.stderr}")
+    return CMP_LIB
 
 
 def headers() -> list[Path]:
@@ -113,6 +131,7 @@ def main(argv=None) -> int:
     print(build(ns.force, ns.verbose))
     for exe in build_cpp_tests(ns.verbose):
         print(exe)
+    print(build_comparator())
     return 0
 
 

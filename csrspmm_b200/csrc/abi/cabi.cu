@@ -55,12 +55,12 @@ void launch_merge(const SpmmParams& p, const Plan& plan, cudaStream_t st)
 template <int NV, int FMT>
 cudaError_t launch_tma(const SpmmParams& p, const Plan& plan, cudaStream_t st)
 {
-    auto kern = spmm_tma_kernel<NV, 128, 8, FMT>;
+    auto kern = spmm_tma_kernel<NV, CSRSPMM_TUNE_TMA_TG, CSRSPMM_TUNE_TMA_SLOTS, FMT>;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int)plan.dynamic_smem);
     if (e != cudaSuccess) return e;
-    const unsigned slot = (unsigned)(plan.dynamic_smem / (8 * 8));
-    kern<<<(unsigned)plan.grid, kMergeThreads, plan.dynamic_smem, st>>>(p, slot);
+    kern<<<(unsigned)plan.grid, kMergeThreads, plan.dynamic_smem, st>>>(p, (unsigned)plan.tma_slot_bytes,
+                                                                        (unsigned)(plan.dynamic_smem / 8));
     return cudaSuccess;
 }
 

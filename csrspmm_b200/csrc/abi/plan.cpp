@@ -137,14 +137,20 @@ int make_plan(const csrspmm_b200_args* a, Plan* plan)
         if (kernel == CSRSPMM_B200_KERNEL_TMA && !tma_can_run(a)) kernel = CSRSPMM_B200_KERNEL_AUTO;
     }
     if (kernel == CSRSPMM_B200_KERNEL_AUTO) {
+        // Measured on B200 (profiles/): the bulk-copy path completes about one row copy per 80
+        // cycles per SM, so it only keeps HBM busy when a row of B is 2 KB (384 < Nd <= 512),
+        // where it is 3-4 % ahead of the merge kernel -- provided B is far larger than L2, since
+        // an L2-resident B is served faster through the load/store units.  Whole-row mapping
+        // wins when the longest row is known and close to the mean; everything else (unknown
+        // or skewed row lengths) takes the merge-path kernel.  The entry point asked for does
+        // not change the choice.
         const double avg = a->M > 0 ? (double)a->nnz / (double)a->M : 0.0;
-        const bool smem_entry = a->entry == CSRSPMM_B200_ENTRY_WARP_PER_ROW_SMEM ||
-                                a->entry == CSRSPMM_B200_ENTRY_WARP_PER_ROW_SMEM_FP4 ||
-                                a->entry == CSRSPMM_B200_ENTRY_NAIVE_SMEM;
         const double row_limit = avg * 4.0 > 64.0 ? avg * 4.0 : 64.0;
-        if (smem_entry && tma_can_run(a) && a->Nd >= 64)
+        const double b_bytes = (double)a->Kd * (double)a->Nd * 4.0;
+        const bool rows_even = a->max_row_nnz > 0 && (double)a->max_row_nnz <= row_limit;
+        if (tma_can_run(a) && a->Nd > 384 && b_bytes >= 1073741824.0 && !rows_even)
             kernel = CSRSPMM_B200_KERNEL_TMA;
-        else if (a->max_row_nnz > 0 && (double)a->max_row_nnz <= row_limit)
+        else if (rows_even)
             kernel = CSRSPMM_B200_KERNEL_ROW;
         else
             kernel = CSRSPMM_B200_KERNEL_MERGE;
@@ -161,9 +167,12 @@ int make_plan(const csrspmm_b200_args* a, Plan* plan)
         plan->G = 32;
         plan->NV = plan->ncolv <= 32 ? 1 : (plan->ncolv <= 64 ? 2 : 4);
         plan->shape = plan->NV == 1 ? 2 : (plan->NV == 2 ? 3 : 4);
-        fill_split_geometry(a, plan, 8 * 128);
+        fill_split_geometry(a, plan, 8 * CSRSPMM_TUNE_TMA_TG);
         const size_t slot = align_up((size_t)a->Nd * 4, 128);
-        plan->dynamic_smem = 8 /*warps*/ * 8 /*slots*/ * slot;
+        size_t ring = (size_t)CSRSPMM_TUNE_TMA_SLOTS * slot;          // per warp
+        if (ring < (size_t)512 * plan->NV) ring = (size_t)512 * plan->NV;  // must also hold the partial sums
+        plan->tma_slot_bytes = slot;
+        plan->dynamic_smem = 8 /*warps*/ * ring;
     } else {
         plan->shape = shape_for(plan->ncolv);
         plan->G = kShapes[plan->shape].G;
@@ -187,7 +196,7 @@ size_t worst_case_workspace(const csrspmm_b200_args* a)
 {
     if (check_args(a, false) != CSRSPMM_B200_OK) return 0;
     // sized for the smallest tile any split kernel uses (most CTAs, most carry rows)
-    int tile = 8 * 128;  // TMA kernel
+    int tile = 8 * CSRSPMM_TUNE_TMA_TG;  // TMA kernel
     for (int k = 0; k < kNumShapes; ++k) {
         const int t = (256 / kShapes[k].G) * kShapes[k].TG;
         if (t < tile) tile = t;

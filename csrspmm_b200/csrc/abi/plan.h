@@ -26,7 +26,8 @@ struct Plan {
     long long carry_ld = 0;                // floats per carry row
     size_t carry_row_bytes = 0;            // 256-byte aligned
     size_t workspace_bytes = 0;            // carry_row_bytes + carry values
-    size_t dynamic_smem = 0;               // TMA kernel only
+    size_t dynamic_smem = 0;               // TMA kernel only: 8 warps x ring_stride
+    size_t tma_slot_bytes = 0;             // TMA kernel only: one row of B rounded up to 128 bytes
 };
 
 // Checks the argument block (sizes, enums, pointers) without touching memory.

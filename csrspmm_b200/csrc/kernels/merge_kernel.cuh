@@ -83,6 +83,7 @@ struct MergeSmem {
     int coord[4];
     int tail_row[GROUPS];
     alignas(16) float tail[GROUPS][ROWW];
+    __device__ __forceinline__ float* tail_of(int g) { return tail[g]; }
 };
 
 // Where a lane group's share of the tile starts and ends, in tile-local coordinates.
@@ -164,7 +165,7 @@ __device__ __forceinline__ void merge_tile_finish(const SpmmParams& p, Smem& s, 
     if (lane == 0) s.tail_row[g] = dirty ? r.il1 : -1;
     if (dirty) {
 #pragma unroll
-        for (int v = 0; v < NV; ++v) acc[v].store(&s.tail[g][(lane + v * G) * VW]);
+        for (int v = 0; v < NV; ++v) acc[v].store(s.tail_of(g) + (lane + v * G) * VW);
     }
     __syncthreads();
 
@@ -175,12 +176,12 @@ __device__ __forceinline__ void merge_tile_finish(const SpmmParams& p, Smem& s, 
         if (gs < g) {
             Vec<VW> sum[NV];
 #pragma unroll
-            for (int v = 0; v < NV; ++v) sum[v].load(&s.tail[gs][(lane + v * G) * VW]);
+            for (int v = 0; v < NV; ++v) sum[v].load(s.tail_of(gs) + (lane + v * G) * VW);
             for (int q = gs + 1; q < g; ++q) {
 #pragma unroll
                 for (int v = 0; v < NV; ++v) {
                     Vec<VW> t;
-                    t.load(&s.tail[q][(lane + v * G) * VW]);
+                    t.load(s.tail_of(q) + (lane + v * G) * VW);
                     sum[v].add(t);
                 }
             }
@@ -205,10 +206,10 @@ __device__ __forceinline__ void merge_tile_finish(const SpmmParams& p, Smem& s, 
                 const int cv = cb + lane + v * G;
                 if (cv < p.ncolv) {
                     Vec<VW> sum;
-                    sum.load(&s.tail[gs][(lane + v * G) * VW]);
+                    sum.load(s.tail_of(gs) + (lane + v * G) * VW);
                     for (int q = gs + 1; q < GROUPS; ++q) {
                         Vec<VW> t;
-                        t.load(&s.tail[q][(lane + v * G) * VW]);
+                        t.load(s.tail_of(q) + (lane + v * G) * VW);
                         sum.add(t);
                     }
                     sum.store(crow + (long long)cv * VW);

@@ -81,7 +81,9 @@ __device__ __forceinline__ void fence_mbar_init()
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
 }
 
-// Static part of the shared memory (the ring itself is dynamic: kTmaWarps * SLOTS * slot_bytes).
+// Static part of the shared memory.  The ring is dynamic: kTmaWarps * ring_stride bytes with
+// ring_stride = max(SLOTS * slot_bytes, 512 * NV), so that a warp's ring can also hold the
+// 32 * NV float4 of its partial sums once its copies have all been consumed.
 template <int NV, int TG, int SLOTS>
 struct TmaSmem {
     static constexpr int GROUPS = kTmaWarps;
@@ -91,13 +93,15 @@ struct TmaSmem {
     alignas(8) int2 cv[TILE];  // (column index, value bits) of each staged non-zero
     int coord[4];
     int tail_row[GROUPS];
-    alignas(16) float tail[GROUPS][ROWW];
+    float* tail_ptr[GROUPS];  // each warp's partial-sum row lives in its own (by then idle) ring
     alignas(8) unsigned long long bar[GROUPS][SLOTS];
+    __device__ __forceinline__ float* tail_of(int g) { return tail_ptr[g]; }
 };
 
 // NV float4 per lane cover the whole row (Nd <= 128 * NV), so there is a single column pass.
 template <int NV, int TG, int SLOTS, int FMT>
-__global__ void __launch_bounds__(kMergeThreads) spmm_tma_kernel(const SpmmParams p, unsigned slot_bytes)
+__global__ void __launch_bounds__(kMergeThreads, CSRSPMM_TUNE_TMA_MINB) spmm_tma_kernel(const SpmmParams p, unsigned slot_bytes,
+                                                                                         unsigned ring_stride)
 {
     constexpr int G = 32, VW = 4;
     using Smem = TmaSmem<NV, TG, SLOTS>;
@@ -106,7 +110,9 @@ __global__ void __launch_bounds__(kMergeThreads) spmm_tma_kernel(const SpmmParam
 
     const int g = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
+    unsigned char* my_ring = ring + (size_t)g * ring_stride;
     if (lane == 0) {
+        s.tail_ptr[g] = reinterpret_cast<float*>(my_ring);
 #pragma unroll
         for (int k = 0; k < SLOTS; ++k) mbar_init(smem_u32(&s.bar[g][k]), 1);
         fence_mbar_init();
@@ -118,7 +124,6 @@ __global__ void __launch_bounds__(kMergeThreads) spmm_tma_kernel(const SpmmParam
     if (!merge_tile_setup<Smem, G, TG, FMT>(p, s, r)) return;
 
     const unsigned row_bytes = (unsigned)p.Nd * 4u;
-    unsigned char* my_ring = ring + (size_t)g * SLOTS * slot_bytes;
     const unsigned ring_base = smem_u32(my_ring);
     const unsigned bar_base = smem_u32(&s.bar[g][0]);
 

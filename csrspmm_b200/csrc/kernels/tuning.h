@@ -34,6 +34,18 @@
 #define CSRSPMM_TUNE_C_STREAMING 0
 #endif
 
+// shared-memory row buffers per warp in the TMA kernel (bulk copies in flight per warp)
+#ifndef CSRSPMM_TUNE_TMA_SLOTS
+#define CSRSPMM_TUNE_TMA_SLOTS 4
+#endif
+// merge-path items per warp in the TMA kernel, and its requested CTAs per SM
+#ifndef CSRSPMM_TUNE_TMA_TG
+#define CSRSPMM_TUNE_TMA_TG 128
+#endif
+#ifndef CSRSPMM_TUNE_TMA_MINB
+#define CSRSPMM_TUNE_TMA_MINB 2
+#endif
+
 // minimum resident CTAs per SM requested from the compiler (caps registers per thread)
 #ifndef CSRSPMM_TUNE_MERGE_MINB_NV1
 #define CSRSPMM_TUNE_MERGE_MINB_NV1 4

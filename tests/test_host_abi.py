@@ -73,13 +73,17 @@ def test_kernel_selection():
     # unknown or skewed row lengths -> merge-path
     assert sel(16384, 16384, 128, 268000) == "merge"
     assert sel(1 << 20, 1 << 20, 64, 16_000_000, max_row_nnz=16384) == "merge"
-    # shared-memory entry points with a 16-byte layout -> TMA-staged kernel
-    assert sel(65536, 65536, 256, 21_000_000, entry="warp_per_row_smem", max_row_nnz=400) == "tma"
-    assert sel(65536, 65536, 256, 21_000_000, entry="warp_per_row_smem_fp4") == "tma"
-    # ... but not when rows of B are not 16-byte aligned, or too wide for one pass
-    assert sel(100, 100, 66, 1000, entry="warp_per_row_smem") == "merge"
-    assert sel(100, 100, 1024, 1000, entry="warp_per_row_smem") == "merge"
-    assert sel(100, 100, 256, 1000, entry="warp_per_row_smem", aligned=False) == "merge"
+    # 2 KB rows of a B far larger than L2 -> bulk-copy (TMA) kernel, whatever the entry point
+    assert sel(1 << 22, 1 << 22, 512, 134_000_000) == "tma"
+    assert sel(1 << 22, 1 << 22, 512, 134_000_000, entry="warp_per_row_smem_fp4", max_row_nnz=65536) == "tma"
+    assert sel(1 << 22, 1 << 22, 400, 134_000_000) == "tma"
+    # ... but not for narrower rows, an L2-sized B, even rows, or a layout without 16-byte rows
+    assert sel(1 << 22, 1 << 22, 256, 134_000_000) == "merge"
+    assert sel(65536, 65536, 512, 21_000_000) == "merge"
+    assert sel(1 << 22, 1 << 22, 512, 134_000_000, max_row_nnz=40) == "row"
+    assert sel(1 << 22, 1 << 22, 510, 134_000_000) == "merge"
+    assert sel(1 << 22, 1 << 22, 512, 134_000_000, aligned=False) == "merge"
+    assert sel(65536, 65536, 256, 21_000_000, entry="warp_per_row_smem", max_row_nnz=400) == "row"
     # pinned kernels are honoured or refused, never silently replaced
     assert sel(100, 100, 64, 1000, kernel="row") == "row"
     assert sel(100, 100, 64, 1000, kernel="tma") == "tma"
