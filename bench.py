@@ -411,37 +411,56 @@ def main(argv=None):
         got = C_out[torch.from_numpy(rows).to(dev)].cpu().numpy()
         check = bool((np.abs(got - f64) <= 1e-5 * mag + 1e-6).all())
 
-    # ---- end to end: pinned host buffers through csrspmm_b200_spmm_host ------------------------------
+    # ---- end to end: pinned host buffers in, host C out ---------------------------------------------
+    # N = 1: csrspmm_b200_spmm_host (one C-ABI call does the copies and the product).
+    # N > 1: distributed.ShardedHostSpmm -- each rank uploads its block of A and 1/N of B, the
+    #        slices of B are all-gathered over NVLink, C blocks go back to their hosts.
     e2e = None
     if not ns.no_extras:
-        h = {k: torch.empty(v.shape, dtype=v.dtype, pin_memory=True) for k, v in t.items()}
-        for k in h:
-            h[k].copy_(t[k])
-        C_host = torch.empty((my_rows, Nd), dtype=torch.float32, pin_memory=True)
-        arena = torch.empty(ops.host_arena_bytes(my_rows, Kd, Nd, my_nnz), dtype=torch.uint8, device=dev)
+        keep_rows = torch.arange(0, my_rows, max(my_rows // 4096, 1), device=dev)
+        keep_vals = C_out[keep_rows].clone()  # the device-timed result on a row sample, to compare e2e against
+        if world == 1:
+            h = {k: torch.empty(v.shape, dtype=v.dtype, pin_memory=True) for k, v in t.items()}
+            for k in h:
+                h[k].copy_(t[k])
+            C_host = torch.empty((my_rows, Nd), dtype=torch.float32, pin_memory=True)
+            arena = torch.empty(ops.host_arena_bytes(my_rows, Kd, Nd, my_nnz), dtype=torch.uint8, device=dev)
+
+            def e2e_step():
+                ops.spmm_host(h["row_ptr"], h["col_idx"], h["values"], h["B"], C_host, 1.0, 0.0, kernel=ns.kernel,
+                              arena=arena, device=dev)
+
+            h2d = my_nnz * 8 + (my_rows + 1) * 4 + Kd * Nd * 4
+            d2h, xchg = my_rows * Nd * 4, 0
+            api = "csrspmm_b200_spmm_host (pinned host A, B in; host C out)"
+        else:
+            sl = Kd // world
+            hs = D.Shard(rank, world, shard.row_lo, shard.row_hi,
+                         shard.row_ptr.cpu().pin_memory(), shard.col_idx.cpu().pin_memory(),
+                         shard.values.cpu().pin_memory(), shard.max_row_nnz)
+            hB = B[rank * sl:(rank + 1) * sl].cpu().pin_memory()
+            del t, B, shard, C_out, workspace
+            torch.cuda.empty_cache()
+            runner = D.ShardedHostSpmm(hs, hB, Kd, dev, kernel=ns.kernel)
+            e2e_step = runner.run
+            h2d, d2h, xchg = runner.h2d_bytes, runner.d2h_bytes, runner.exchange_bytes
+            api = ("distributed.ShardedHostSpmm (per rank: pinned host block of A and 1/N of B in, NCCL all-gather of "
+                   "B, host block of C out)")
         torch.cuda.synchronize()
-
-        def e2e_step():
-            ops.spmm_host(h["row_ptr"], h["col_idx"], h["values"], h["B"], C_host, 1.0, 0.0, kernel=ns.kernel,
-                          arena=arena, device=dev)
-
         e2e_step()  # warm-up
         barrier()
         t0 = time.perf_counter()
-        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        ev0.record()
         for _ in range(ns.e2e_steps):
             e2e_step()
-        ev1.record()
         torch.cuda.synchronize()
-        e2e_sec = max(ev0.elapsed_time(ev1) / 1e3, time.perf_counter() - t0) / ns.e2e_steps
+        e2e_sec = (time.perf_counter() - t0) / ns.e2e_steps
         e2e_sec = D.max_over_ranks(e2e_sec, dev)
-        h2d = my_nnz * 8 + (my_rows + 1) * 4 + Kd * Nd * 4
-        d2h = my_rows * Nd * 4
-        e2e = {"value": flops_total / e2e_sec / 1e9, "unit": "GFLOPS", "h2d_bytes_per_step": int(h2d),
-               "d2h_bytes_per_step": int(d2h), "ms_per_step": e2e_sec * 1e3, "steps": ns.e2e_steps,
-               "api": "csrspmm_b200_spmm_host (pinned host A, B in; host C out)"}
-        del h, C_host, arena
+        C_e2e = C_host if world == 1 else runner.C_host
+        same = bool(torch.equal(C_e2e[keep_rows.cpu()], keep_vals.cpu()))
+        same = D.sum_over_ranks(0.0 if same else 1.0, dev) == 0.0
+        e2e = {"value": flops_total / e2e_sec / 1e9, "equals_device_run": same, "unit": "GFLOPS", "h2d_bytes_per_step": int(h2d),
+               "d2h_bytes_per_step": int(d2h), "nvlink_bytes_per_step": int(xchg), "ms_per_step": e2e_sec * 1e3,
+               "steps": ns.e2e_steps, "bytes_are": "per rank", "api": api}
 
     if world > 1:
         barrier()

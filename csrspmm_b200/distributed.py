@@ -8,6 +8,10 @@ rank keeps its block of A re-based to local offsets (column indices unchanged) a
 B that is broadcast ONCE, outside any timed region, and every rank multiplies its block with the
 single-GPU kernels.  C stays sharded.  ``torch.distributed`` (NCCL on GPUs, gloo on CPU for the
 host-logic tests) provides the broadcast, the barrier and the max-over-ranks reduction of times.
+
+When the operands start in HOST memory (``ShardedHostSpmm``) there is one real exchange: each rank
+uploads only 1/N of B over PCIe and the slices are all-gathered over NVLink, instead of every
+rank pulling all of B through its own PCIe link.
 """
 from __future__ import annotations
 
@@ -95,6 +99,54 @@ def sum_over_ranks(value: float, device) -> float:
     if dist.is_initialized() and dist.get_world_size() > 1:
         dist.all_reduce(t, op=dist.ReduceOp.SUM)
     return float(t.item())
+
+
+class ShardedHostSpmm:
+    """End-to-end product from HOST memory on several GPUs: every rank uploads only its own part.
+
+    Rank g holds, in pinned host memory, its row block of A and rows [g*Kd/world, (g+1)*Kd/world)
+    of B.  One ``run()`` = upload the block of A and the slice of B, all-gather the slices over
+    NVLink into the full device copy of B (the one exchange this path has: each byte of B
+    crosses PCIe once instead of once per GPU), multiply, download the block of C.  With a
+    single rank there is no exchange and this is the plain host round trip.
+    """
+
+    def __init__(self, shard_host: "Shard", B_slice_host: torch.Tensor, Kd: int, device, kernel: str = "auto"):
+        import torch.distributed as dist
+        from . import ops
+        self.dist, self.ops, self.dev = dist, ops, torch.device(device)
+        self.world = dist.get_world_size() if dist.is_initialized() else 1
+        self.rank = dist.get_rank() if dist.is_initialized() else 0
+        if Kd % self.world != 0 or B_slice_host.shape[0] * self.world != Kd:
+            raise ValueError("Kd must be divisible by the number of ranks and B_slice_host hold Kd/world rows")
+        self.h_rp, self.h_ci, self.h_va, self.h_B = shard_host.row_ptr, shard_host.col_idx, shard_host.values, B_slice_host
+        Nd, rows = B_slice_host.shape[1], shard_host.rows
+        d = self.dev
+        self.d_rp = torch.empty(rows + 1, dtype=torch.int32, device=d)
+        self.d_ci = torch.empty(shard_host.nnz, dtype=torch.int32, device=d)
+        self.d_va = torch.empty(shard_host.nnz, dtype=torch.float32, device=d)
+        self.d_B = torch.empty((Kd, Nd), dtype=torch.float32, device=d)
+        self.d_C = torch.empty((rows, Nd), dtype=torch.float32, device=d)
+        self.C_host = torch.empty((rows, Nd), dtype=torch.float32, pin_memory=True)
+        self.slice_rows = Kd // self.world
+        self.call = ops.SpmmCall(self.d_rp, self.d_ci, self.d_va, self.d_B, self.d_C, 1.0, 0.0, kernel=kernel)
+        self.h2d_bytes = (rows + 1) * 4 + shard_host.nnz * 8 + self.slice_rows * Nd * 4
+        self.d2h_bytes = rows * Nd * 4
+        self.exchange_bytes = (Kd - self.slice_rows) * Nd * 4  # received over NVLink per rank
+
+    def run(self) -> torch.Tensor:
+        k0 = self.rank * self.slice_rows
+        mine = self.d_B[k0:k0 + self.slice_rows]
+        self.d_rp.copy_(self.h_rp, non_blocking=True)
+        self.d_ci.copy_(self.h_ci, non_blocking=True)
+        self.d_va.copy_(self.h_va, non_blocking=True)
+        mine.copy_(self.h_B, non_blocking=True)
+        if self.world > 1:
+            self.dist.all_gather_into_tensor(self.d_B, mine)  # in place: slice g already sits at offset g
+        self.call()
+        self.C_host.copy_(self.d_C, non_blocking=True)
+        torch.cuda.current_stream(self.dev).synchronize()
+        return self.C_host
 
 
 def partition_imbalance(row_ptr, bounds, row_weight: float = 1.0) -> float:
