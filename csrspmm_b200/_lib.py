@@ -34,7 +34,8 @@ EXPORTED_SYMBOLS = (
     "csrspmm_b200_host_arena_bytes", "csrspmm_b200_workspace_bytes", "csrspmm_b200_select_kernel",
     "csrspmm_b200_validate_csr_host", "csrspmm_b200_validate_csr_device",
     "csrspmm_b200_row_stats_device", "csrspmm_b200_partition_rows", "csrspmm_b200_e2m1_scale",
-    "csrspmm_b200_e2m1_encode", "csrspmm_b200_e2m1_decode",
+    "csrspmm_b200_e2m1_encode", "csrspmm_b200_e2m1_decode", "csrspmm_b200_dense2csr_count",
+    "csrspmm_b200_dense2csr_fill", "csrspmm_b200_csr2dense",
 )
 
 
@@ -124,6 +125,15 @@ def lib() -> C.CDLL:
     L.csrspmm_b200_e2m1_encode.restype = C.c_int
     L.csrspmm_b200_e2m1_decode.argtypes = [C.c_int64, C.c_void_p, C.c_float, C.c_void_p]
     L.csrspmm_b200_e2m1_decode.restype = C.c_int
+    L.csrspmm_b200_dense2csr_count.argtypes = [C.c_int32, C.c_int32, C.c_void_p, C.c_int64, C.c_float, C.c_void_p,
+                                               C.POINTER(C.c_int64), C.POINTER(C.c_int32), C.c_void_p]
+    L.csrspmm_b200_dense2csr_count.restype = C.c_int
+    L.csrspmm_b200_dense2csr_fill.argtypes = [C.c_int32, C.c_int32, C.c_void_p, C.c_int64, C.c_float, C.c_void_p,
+                                              C.c_void_p, C.c_void_p, C.c_void_p]
+    L.csrspmm_b200_dense2csr_fill.restype = C.c_int
+    L.csrspmm_b200_csr2dense.argtypes = [C.c_int32, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64,
+                                         C.c_void_p]
+    L.csrspmm_b200_csr2dense.restype = C.c_int
     if L.csrspmm_b200_abi_version() != 1:
         raise LibraryMissing(f"{LIB_PATH} has ABI version {L.csrspmm_b200_abi_version()}, expected 1")
     _lib = L

@@ -9,6 +9,8 @@
 #include <csrspmm/error_check.h>
 #include <csrspmm/matrix.h>
 
+#include "csrspmm_b200.h"
+
 #include <algorithm>
 #include <cmath>
 #include <cstdio>
@@ -169,6 +171,42 @@ void csr_device2host(const CSRMatrix& dA, CSRMatrix& hA)
     cudaCheck(cudaMemcpy(hA.row_ptr, dA.row_ptr, rowptr_bytes(dA.height), cudaMemcpyDeviceToHost));
     cudaCheck(cudaMemcpy(hA.col_idx, dA.col_idx, size_t(dA.nnz) * sizeof(int), cudaMemcpyDeviceToHost));
     cudaCheck(cudaMemcpy(hA.values, dA.values, size_t(dA.nnz) * sizeof(float), cudaMemcpyDeviceToHost));
+}
+
+void dense2csr_device(const DenseMatrix& d_dense, CSRMatrix& d_csr, float tol)
+{
+    if (!d_dense.data || d_dense.height <= 0 || d_dense.width <= 0) die("dense2csr_device: invalid dense matrix");
+    if (any_pointer(d_csr)) die("dense2csr_device error: destination must be null.");
+    int* row_ptr = nullptr;
+    cudaCheck(cudaMalloc(reinterpret_cast<void**>(&row_ptr), rowptr_bytes(d_dense.height)));
+    int64_t nnz = 0;
+    int32_t longest = 0;
+    if (csrspmm_b200_dense2csr_count(d_dense.height, d_dense.width, d_dense.data, d_dense.width, tol, row_ptr, &nnz,
+                                     &longest, nullptr) != CSRSPMM_B200_OK)
+        die(csrspmm_b200_last_error());
+    set_dims(d_csr, d_dense.height, d_dense.width, int(nnz));
+    d_csr.row_ptr = row_ptr;
+    d_csr.max_row_nnz = longest;
+    cudaCheck(cudaMalloc(reinterpret_cast<void**>(&d_csr.col_idx), std::max<size_t>(size_t(nnz) * sizeof(int), 4)));
+    cudaCheck(cudaMalloc(reinterpret_cast<void**>(&d_csr.values), std::max<size_t>(size_t(nnz) * sizeof(float), 4)));
+    if (csrspmm_b200_dense2csr_fill(d_dense.height, d_dense.width, d_dense.data, d_dense.width, tol, d_csr.row_ptr,
+                                    d_csr.col_idx, d_csr.values, nullptr) != CSRSPMM_B200_OK)
+        die(csrspmm_b200_last_error());
+    cudaCheck(cudaDeviceSynchronize());
+}
+
+void csr2dense_device(const CSRMatrix& d_csr, DenseMatrix& d_dense)
+{
+    if (!all_pointers(d_csr) || d_csr.height <= 0 || d_csr.width <= 0) die("csr2dense_device: invalid csr");
+    if (d_dense.data != nullptr) die("csr2dense_device error: destination must be null.");
+    d_dense.height = d_csr.height;
+    d_dense.width = d_csr.width;
+    cudaCheck(cudaMalloc(reinterpret_cast<void**>(&d_dense.data),
+                         size_t(d_csr.height) * size_t(d_csr.width) * sizeof(float)));
+    if (csrspmm_b200_csr2dense(d_csr.height, d_csr.width, d_csr.row_ptr, d_csr.col_idx, d_csr.values, d_dense.data,
+                               d_csr.width, nullptr) != CSRSPMM_B200_OK)
+        die(csrspmm_b200_last_error());
+    cudaCheck(cudaDeviceSynchronize());
 }
 
 }  // namespace csrspmm

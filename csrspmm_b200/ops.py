@@ -282,3 +282,38 @@ def spmm_host(row_ptr, col_idx, values, B, C_host, alpha=1.0, beta=0.0, *, entry
 def host_arena_bytes(M, Kd, Nd, nnz) -> int:
     a = _lib.make_args(M, Kd, Nd, nnz)
     return int(_lib.lib().csrspmm_b200_host_arena_bytes(C.byref(a)))
+
+
+# ---- dense <-> CSR on the device (csrspmm::dense2csr / csr2dense for device-resident matrices) ----------
+
+def dense2csr(dense: torch.Tensor, tol: float = 0.0):
+    """CUDA float32 matrix -> (row_ptr, col_idx, values, max_row_nnz), the arrays the reference's host
+    ``dense2csr`` would produce (entries with |v| > tol, ascending columns), built on the device."""
+    if not dense.is_cuda or dense.dtype != torch.float32 or dense.dim() != 2 or (dense.stride(1) != 1 and dense.size(1) > 1):
+        raise RuntimeError("dense must be a row-major float32 CUDA matrix")
+    H, W = dense.shape
+    ld = dense.stride(0) if H > 1 else max(W, 1)
+    L = _lib.lib()
+    row_ptr = torch.empty(H + 1, dtype=torch.int32, device=dense.device)
+    nnz, mx = C.c_int64(0), C.c_int32(0)
+    with torch.cuda.device(dense.device):
+        stream = C.c_void_p(torch.cuda.current_stream(dense.device).cuda_stream)
+        _lib.check(L.csrspmm_b200_dense2csr_count(H, W, dense.data_ptr(), max(ld, W), float(tol), row_ptr.data_ptr(),
+                                                  C.byref(nnz), C.byref(mx), stream), "csrspmm_b200_dense2csr_count")
+        col_idx = torch.empty(nnz.value, dtype=torch.int32, device=dense.device)
+        values = torch.empty(nnz.value, dtype=torch.float32, device=dense.device)
+        _lib.check(L.csrspmm_b200_dense2csr_fill(H, W, dense.data_ptr(), max(ld, W), float(tol), row_ptr.data_ptr(),
+                                                 col_idx.data_ptr(), values.data_ptr(), stream),
+                   "csrspmm_b200_dense2csr_fill")
+    return row_ptr, col_idx, values, int(mx.value)
+
+
+def csr2dense(row_ptr: torch.Tensor, col_idx: torch.Tensor, values: torch.Tensor, shape) -> torch.Tensor:
+    """CSR arrays on a CUDA device -> dense float32 matrix of the given shape."""
+    H, W = int(shape[0]), int(shape[1])
+    out = torch.empty((H, W), dtype=torch.float32, device=row_ptr.device)
+    with torch.cuda.device(row_ptr.device):
+        stream = C.c_void_p(torch.cuda.current_stream(row_ptr.device).cuda_stream)
+        _lib.check(_lib.lib().csrspmm_b200_csr2dense(H, W, row_ptr.data_ptr(), col_idx.data_ptr(), values.data_ptr(),
+                                                     out.data_ptr(), max(W, 1), stream), "csrspmm_b200_csr2dense")
+    return out

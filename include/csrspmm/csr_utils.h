@@ -22,4 +22,10 @@ float compression_ratio(const CSRMatrix& csr);
 void csr_host2device(const CSRMatrix& hA, CSRMatrix& dA);
 void csr_device2host(const CSRMatrix& dA, CSRMatrix& hA);
 
+// Additions: the same conversions for matrices that already live on the device (the reference
+// converts on the host only).  d_csr / d_dense must be empty; they are allocated with cudaMalloc
+// and filled with exactly what dense2csr / csr2dense would give for the same data.
+void dense2csr_device(const DenseMatrix& d_dense, CSRMatrix& d_csr, float tol = 0.0f);
+void csr2dense_device(const CSRMatrix& d_csr, DenseMatrix& d_dense);
+
 }  // namespace csrspmm

@@ -21,6 +21,8 @@
  *                               csr_host2device / dense_host2device / spmm / dense_device2host
  *                               (tests/test_csrspmm.cu:80-92, benchmarks/bench_csrspmm.cu:84-91)
  *   csrspmm_b200_select_kernel  the (stub) auto-selection in src/csrspmm.cpp:34-40
+ *   csrspmm_b200_dense2csr_count/_fill, _csr2dense   csrspmm::dense2csr / csr2dense,
+ *                               src/host/csr_utils.cpp:70-145, on device-resident matrices
  *   validate / row_stats / partition_rows / e2m1_*   no counterpart in the reference
  */
 #ifndef CSRSPMM_B200_H
@@ -168,6 +170,23 @@ int csrspmm_b200_validate_csr_device(int32_t M, int32_t Kd, int64_t nnz, const i
  * 32 * (mean + 1), stats[3] = nnz held by those rows.  Waits for the stream. */
 int csrspmm_b200_row_stats_device(int32_t M, const int32_t* row_ptr, int64_t stats[4],
                                   csrspmm_b200_stream_t stream);
+
+/* ---- dense <-> CSR on the device --------------------------------------------------------------
+ * Same results as the reference's host-only csrspmm::dense2csr / csr2dense
+ * (src/host/csr_utils.cpp:70-145): entries with fabs(v) > tol are kept, columns ascending,
+ * max_row_nnz = longest row; the way back zero-fills and scatters.  All pointers are device
+ * pointers, `ld` is the leading dimension of the dense matrix in elements.
+ * Two steps because the caller owns the buffers: _count fills row_ptr (H + 1 entries) and
+ * returns nnz (it waits for the stream); the caller allocates col_idx / values; _fill writes
+ * them (asynchronous). */
+int csrspmm_b200_dense2csr_count(int32_t H, int32_t W, const float* dense, int64_t ld, float tol,
+                                 int32_t* row_ptr, int64_t* nnz_out, int32_t* max_row_nnz_out,
+                                 csrspmm_b200_stream_t stream);
+int csrspmm_b200_dense2csr_fill(int32_t H, int32_t W, const float* dense, int64_t ld, float tol,
+                                const int32_t* row_ptr, int32_t* col_idx, float* values,
+                                csrspmm_b200_stream_t stream);
+int csrspmm_b200_csr2dense(int32_t H, int32_t W, const int32_t* row_ptr, const int32_t* col_idx,
+                           const float* values, float* dense, int64_t ld, csrspmm_b200_stream_t stream);
 
 /* ---- multi-GPU row partition (new) ------------------------------------------------------------
  * Contiguous row blocks [bounds[g], bounds[g+1]) for g < parts with near-equal cost, where the

@@ -59,6 +59,27 @@ static void run_case(int M, int N, int K, float sparsity, float alpha, float bet
     csr_free_host(hA_again);
     EXPECT(hA_again.row_ptr == nullptr && hA_again.height == 0);
 
+    // device-side conversions give the same arrays as the host ones
+    {
+        DenseMatrix dA_dense, dBack, hBack;
+        dense_host2device(hA, dA_dense);
+        CSRMatrix dA2, hA2;
+        dense2csr_device(dA_dense, dA2, 0.0f);
+        csr_device2host(dA2, hA2);
+        EXPECT(hA2.nnz == hA_csr.nnz && hA2.max_row_nnz == hA_csr.max_row_nnz);
+        EXPECT(std::memcmp(hA2.row_ptr, hA_csr.row_ptr, sizeof(int) * size_t(M + 1)) == 0);
+        EXPECT(std::memcmp(hA2.col_idx, hA_csr.col_idx, sizeof(int) * size_t(hA_csr.nnz)) == 0);
+        EXPECT(std::memcmp(hA2.values, hA_csr.values, sizeof(float) * size_t(hA_csr.nnz)) == 0);
+        csr2dense_device(dA2, dBack);
+        dense_device2host(dBack, hBack);
+        EXPECT(dense_compare(hA, hBack, 0.0f));
+        dense_free_host(hBack);
+        dense_free_device(dBack);
+        dense_free_device(dA_dense);
+        csr_free_device(dA2);
+        csr_free_host(hA2);
+    }
+
     DenseMatrix dB;
     dense_host2device(hB, dB);
     for (const char* name : names) {
