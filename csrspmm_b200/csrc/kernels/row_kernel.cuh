@@ -23,7 +23,7 @@ constexpr int kRowThreads = 256;
 
 // FULL: one pass covers the row exactly (G * NV == ncolv), so no column guard is compiled in.
 template <int G, int NV, int VW, int U, int FMT, bool FULL>
-__global__ void __launch_bounds__(kRowThreads, CSRSPMM_TUNE_ROW_MINB) spmm_row_kernel(const SpmmParams p)
+__global__ void __launch_bounds__(kRowThreads, row_min_blocks(NV)) spmm_row_kernel(const SpmmParams p)
 {
     constexpr int GROUPS = kRowThreads / G;
     const cg::thread_block_tile<G> tile = cg::tiled_partition<G>(cg::this_thread_block());

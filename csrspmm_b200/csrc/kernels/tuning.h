@@ -18,7 +18,7 @@
 #define CSRSPMM_TUNE_ROW_U_NV1 4
 #endif
 #ifndef CSRSPMM_TUNE_ROW_U_NV2
-#define CSRSPMM_TUNE_ROW_U_NV2 4
+#define CSRSPMM_TUNE_ROW_U_NV2 2
 #endif
 #ifndef CSRSPMM_TUNE_ROW_U_NV4
 #define CSRSPMM_TUNE_ROW_U_NV4 4
@@ -56,8 +56,14 @@
 #ifndef CSRSPMM_TUNE_MERGE_MINB_NV4
 #define CSRSPMM_TUNE_MERGE_MINB_NV4 2
 #endif
-#ifndef CSRSPMM_TUNE_ROW_MINB
-#define CSRSPMM_TUNE_ROW_MINB 1
+#ifndef CSRSPMM_TUNE_ROW_MINB_NV1
+#define CSRSPMM_TUNE_ROW_MINB_NV1 4
+#endif
+#ifndef CSRSPMM_TUNE_ROW_MINB_NV2
+#define CSRSPMM_TUNE_ROW_MINB_NV2 4
+#endif
+#ifndef CSRSPMM_TUNE_ROW_MINB_NV4
+#define CSRSPMM_TUNE_ROW_MINB_NV4 2
 #endif
 
 // lane-group shapes by dense width class k (column vectors per row <= 8, 16, 32, 64, more):
@@ -121,6 +127,7 @@ constexpr ShapeDesc kShapes[kNumShapes] = {
 
 constexpr int merge_unroll(int nv) { return nv == 1 ? CSRSPMM_TUNE_MERGE_U_NV1 : (nv == 2 ? CSRSPMM_TUNE_MERGE_U_NV2 : CSRSPMM_TUNE_MERGE_U_NV4); }
 constexpr int row_unroll(int nv) { return nv == 1 ? CSRSPMM_TUNE_ROW_U_NV1 : (nv == 2 ? CSRSPMM_TUNE_ROW_U_NV2 : CSRSPMM_TUNE_ROW_U_NV4); }
+constexpr int row_min_blocks(int nv) { return nv == 1 ? CSRSPMM_TUNE_ROW_MINB_NV1 : (nv == 2 ? CSRSPMM_TUNE_ROW_MINB_NV2 : CSRSPMM_TUNE_ROW_MINB_NV4); }
 constexpr int merge_min_blocks(int nv) { return nv == 1 ? CSRSPMM_TUNE_MERGE_MINB_NV1 : (nv == 2 ? CSRSPMM_TUNE_MERGE_MINB_NV2 : CSRSPMM_TUNE_MERGE_MINB_NV4); }
 
 }  // namespace csrspmm_b200

@@ -302,9 +302,10 @@ def dense2csr(dense: torch.Tensor, tol: float = 0.0):
                                                   C.byref(nnz), C.byref(mx), stream), "csrspmm_b200_dense2csr_count")
         col_idx = torch.empty(nnz.value, dtype=torch.int32, device=dense.device)
         values = torch.empty(nnz.value, dtype=torch.float32, device=dense.device)
-        _lib.check(L.csrspmm_b200_dense2csr_fill(H, W, dense.data_ptr(), max(ld, W), float(tol), row_ptr.data_ptr(),
-                                                 col_idx.data_ptr(), values.data_ptr(), stream),
-                   "csrspmm_b200_dense2csr_fill")
+        if nnz.value > 0:
+            _lib.check(L.csrspmm_b200_dense2csr_fill(H, W, dense.data_ptr(), max(ld, W), float(tol), row_ptr.data_ptr(),
+                                                     col_idx.data_ptr(), values.data_ptr(), stream),
+                       "csrspmm_b200_dense2csr_fill")
     return row_ptr, col_idx, values, int(mx.value)
 
 

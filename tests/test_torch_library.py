@@ -67,7 +67,8 @@ def test_gradient_for_b_and_csr_matrix(cuda_lib):
     assert A.max_row_nnz == int(np.diff(p.row_ptr).max()) and A.nnz == p.nnz
     Bg2 = B.clone().requires_grad_(True)
     out2 = A.matmul(Bg2, 0.75)
-    assert torch.equal(out2, out.detach()) or torch.allclose(out2, out.detach(), rtol=1e-5, atol=1e-6)
+    # the holder knows the longest row, so AUTO may pick another kernel: same product, other summation order
+    assert torch.allclose(out2, out.detach(), rtol=1e-4, atol=1e-5)
     (out2 * W).sum().backward()
     assert torch.allclose(Bg2.grad.double(), want_dB, rtol=1e-4, atol=1e-4)
     assert A.t().t() is A and A.t().shape == (p.Kd, p.M)
