@@ -70,6 +70,10 @@ def test_kernel_selection():
     sel = ops.selected_kernel
     # short even rows with a trustworthy max_row_nnz -> row kernel
     assert sel(16384, 16384, 128, 268000, max_row_nnz=38) == "row"
+    # few but long rows: whole-row work cannot fill the chip -> merge-path
+    assert sel(1024, 2048, 128, 419_517, max_row_nnz=470) == "merge"
+    assert sel(512, 1024, 64, 52_205, max_row_nnz=140) == "row"
+    assert sel(4096, 4096, 128, 3_356_995, max_row_nnz=900) == "row"
     # unknown or skewed row lengths -> merge-path
     assert sel(16384, 16384, 128, 268000) == "merge"
     assert sel(1 << 20, 1 << 20, 64, 16_000_000, max_row_nnz=16384) == "merge"
@@ -191,3 +195,16 @@ def test_missing_library_fails_loudly(monkeypatch, tmp_path):
     monkeypatch.setattr(_lib, "LIB_PATH", tmp_path / "nope.so")
     with pytest.raises(_lib.LibraryMissing):
         _lib.lib()
+
+
+def test_sweep_summary_matches_the_reference_summary_definition():
+    # mean GFLOPS per algorithm and mean of per-point speed-ups over cuSPARSE
+    # (the reference's benchmarks/csrspmm_vs_cusparse.py summary)
+    from csrspmm_b200 import sweep
+    rows = [["small", 1, 1, 1, 0.01, 0.99, "csrspmm_b200", "Naive", 100.0],
+            ["small", 1, 1, 1, 0.01, 0.99, "cuSPARSE", "cuSPARSE", 50.0],
+            ["XL", 1, 1, 1, 0.10, 0.90, "csrspmm_b200", "Naive", 300.0],
+            ["XL", 1, 1, 1, 0.10, 0.90, "cuSPARSE", "cuSPARSE", 100.0]]
+    s = {a: (g, sp) for a, g, sp in sweep.summarize(rows)}
+    assert s["Naive"] == (200.0, 2.5) and s["cuSPARSE"] == (75.0, 1.0)
+    assert len(sweep.SHAPES) == 4 and len(sweep.DENSITIES) == 5 and len(sweep.ENTRIES) == 5
