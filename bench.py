@@ -432,7 +432,7 @@ def main(argv=None):
 
             h2d = my_nnz * 8 + (my_rows + 1) * 4 + Kd * Nd * 4
             d2h, xchg = my_rows * Nd * 4, 0
-            api = "csrspmm_b200_spmm_host (pinned host A, B in; host C out)"
+            api = "csrspmm_b200_spmm_host (pinned host A, B in; host C out in row blocks overlapped with compute)"
         else:
             sl = Kd // world
             hs = D.Shard(rank, world, shard.row_lo, shard.row_hi,
@@ -456,9 +456,10 @@ def main(argv=None):
         e2e_sec = (time.perf_counter() - t0) / ns.e2e_steps
         e2e_sec = D.max_over_ranks(e2e_sec, dev)
         C_e2e = C_host if world == 1 else runner.C_host
-        same = bool(torch.equal(C_e2e[keep_rows.cpu()], keep_vals.cpu()))
+        # same product as the device-timed run (row blocks may associate split rows differently)
+        same = bool(torch.allclose(C_e2e[keep_rows.cpu()], keep_vals.cpu(), rtol=1e-3, atol=1e-3))
         same = D.sum_over_ranks(0.0 if same else 1.0, dev) == 0.0
-        e2e = {"value": flops_total / e2e_sec / 1e9, "equals_device_run": same, "unit": "GFLOPS", "h2d_bytes_per_step": int(h2d),
+        e2e = {"value": flops_total / e2e_sec / 1e9, "matches_device_run": same, "unit": "GFLOPS", "h2d_bytes_per_step": int(h2d),
                "d2h_bytes_per_step": int(d2h), "nvlink_bytes_per_step": int(xchg), "ms_per_step": e2e_sec * 1e3,
                "steps": ns.e2e_steps, "bytes_are": "per rank", "api": api}
 

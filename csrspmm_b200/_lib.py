@@ -61,7 +61,7 @@ class Args(C.Structure):
         ("entry", C.c_int32),
         ("kernel", C.c_int32),
         ("max_row_nnz", C.c_int32),
-        ("reserved0", C.c_int32),
+        ("row_ptr_base", C.c_int32),
         ("workspace", C.c_void_p),
         ("workspace_bytes", C.c_size_t),
         ("status_word", C.c_void_p),
@@ -143,7 +143,7 @@ def lib() -> C.CDLL:
 def make_args(M, Kd, Nd, nnz, row_ptr=0, col_idx=0, values=0, B=0, Cptr=0, *, ldb=None, ldc=None,
               alpha=1.0, beta=0.0, entry=ENTRY_NAIVE, kernel=KERNEL_AUTO, max_row_nnz=0,
               value_format=VALUES_F32, value_scale=1.0, workspace=0, workspace_bytes=0,
-              status_word=0) -> Args:
+              status_word=0, row_ptr_base=0) -> Args:
     a = Args()
     a.struct_size = C.sizeof(Args)
     a.M, a.Kd, a.Nd, a.nnz = int(M), int(Kd), int(Nd), int(nnz)
@@ -153,6 +153,7 @@ def make_args(M, Kd, Nd, nnz, row_ptr=0, col_idx=0, values=0, B=0, Cptr=0, *, ld
     a.C, a.ldc = Cptr or None, int(Nd if ldc is None else ldc)
     a.alpha, a.beta = float(alpha), float(beta)
     a.entry, a.kernel, a.max_row_nnz = int(entry), int(kernel), int(max_row_nnz)
+    a.row_ptr_base = int(row_ptr_base)
     a.workspace, a.workspace_bytes = workspace or None, int(workspace_bytes)
     a.status_word = status_word or None
     return a

@@ -117,6 +117,7 @@ int enqueue(const csrspmm_b200_args* a, cudaStream_t st)
     p.ncolv = plan.ncolv;
     p.num_items = plan.num_items;
     p.row_ptr = a->row_ptr;
+    p.rp_base = a->row_ptr_base;
     p.col_idx = a->col_idx;
     p.values = a->values;
     p.value_scale = a->value_scale;
@@ -274,6 +275,10 @@ int csrspmm_b200_spmm_host(const csrspmm_b200_args* a, void* device_arena, size_
     int status = check_args(a, true);
     if (status != CSRSPMM_B200_OK) return status;
     if (a->M == 0 || a->Nd == 0) return CSRSPMM_B200_OK;
+    if (a->row_ptr_base != 0) {
+        set_last_error("spmm_host: row_ptr_base must be 0 (pass the whole matrix)");
+        return CSRSPMM_B200_ERR_BAD_ARG;
+    }
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
     const size_t need = csrspmm_b200_host_arena_bytes(a);
     char* arena = static_cast<char*>(device_arena);
@@ -287,33 +292,54 @@ int csrspmm_b200_spmm_host(const csrspmm_b200_args* a, void* device_arena, size_
         return CSRSPMM_B200_ERR_WORKSPACE;
     }
 
-    const size_t vbytes = a->value_format == CSRSPMM_B200_VALUES_E2M1 ? (size_t)(a->nnz + 1) / 2
-                                                                      : (size_t)a->nnz * 4;
+    const bool e2m1 = a->value_format == CSRSPMM_B200_VALUES_E2M1;
+    const size_t vbytes = e2m1 ? (size_t)(a->nnz + 1) / 2 : (size_t)a->nnz * 4;
     const size_t rp_bytes = ((size_t)a->M + 1) * 4, ci_bytes = (size_t)a->nnz * 4;
     const size_t c_bytes = (size_t)a->M * (size_t)a->Nd * 4;
     const size_t ws_bytes = worst_case_workspace(a);
     char* cur = arena;
     int32_t* d_rp = reinterpret_cast<int32_t*>(cur); cur += align256(rp_bytes);
     int32_t* d_ci = reinterpret_cast<int32_t*>(cur); cur += align256(ci_bytes);
-    void* d_va = cur; cur += align256(vbytes);
+    char* d_va = cur; cur += align256(vbytes);
     float* d_B = reinterpret_cast<float*>(cur); cur += align256((size_t)a->Kd * (size_t)a->Nd * 4);
     float* d_C = reinterpret_cast<float*>(cur); cur += align256(c_bytes);
     void* d_ws = cur; cur += align256(ws_bytes);
     int32_t* d_status = reinterpret_cast<int32_t*>(cur);
 
-    auto fail = [&](int code) {
+    // C goes back in row blocks on a second stream while the next block is being computed, so
+    // the device->host copy of a large C hides the kernel time (and vice versa).
+    constexpr int kMaxBlocks = 8;
+    int blocks = (c_bytes >= ((size_t)64 << 20) && a->M >= 64) ? kMaxBlocks : 1;
+    int32_t bounds[kMaxBlocks + 1] = {0};
+    bounds[1] = a->M;
+    if (blocks > 1 && csrspmm_b200_partition_rows(a->M, a->row_ptr, blocks, 1.0, bounds) != CSRSPMM_B200_OK) blocks = 1;
+    if (blocks > 1 && e2m1)  // packed values can only be offset by whole bytes
+        for (int k = 1; k < blocks; ++k)
+            if (a->row_ptr[bounds[k]] & 1) blocks = 1;
+    if (blocks == 1) bounds[1] = a->M;
+
+    cudaStream_t copy_stream = nullptr;
+    cudaEvent_t done[kMaxBlocks] = {};
+    int events = 0;
+    auto cleanup = [&]() {
+        for (int k = 0; k < events; ++k) cudaEventDestroy(done[k]);
+        if (copy_stream) cudaStreamDestroy(copy_stream);
         if (owned) cudaFreeAsync(arena, st);
-        return code;
     };
 #define CUDA_TRY_HOST(expr)                                                                 \
     do {                                                                                    \
         cudaError_t e__ = (expr);                                                           \
         if (e__ != cudaSuccess) {                                                           \
             set_last_error("%s failed: %s", #expr, cudaGetErrorString(e__));                \
-            return fail(CSRSPMM_B200_ERR_CUDA);                                             \
+            cleanup();                                                                      \
+            return CSRSPMM_B200_ERR_CUDA;                                                   \
         }                                                                                   \
     } while (0)
 
+    if (blocks > 1) {
+        CUDA_TRY_HOST(cudaStreamCreateWithFlags(&copy_stream, cudaStreamNonBlocking));
+        for (; events < blocks; ++events) CUDA_TRY_HOST(cudaEventCreateWithFlags(&done[events], cudaEventDisableTiming));
+    }
     CUDA_TRY_HOST(cudaMemsetAsync(d_status, 0, 4, st));
     CUDA_TRY_HOST(cudaMemcpyAsync(d_rp, a->row_ptr, rp_bytes, cudaMemcpyHostToDevice, st));
     if (a->nnz > 0) {
@@ -329,26 +355,44 @@ int csrspmm_b200_spmm_host(const csrspmm_b200_args* a, void* device_arena, size_
         CUDA_TRY_HOST(cudaMemcpy2DAsync(d_C, (size_t)a->Nd * 4, a->C, (size_t)a->ldc * 4,
                                         (size_t)a->Nd * 4, (size_t)a->M, cudaMemcpyHostToDevice, st));
     }
-    csrspmm_b200_args d = *a;
-    d.row_ptr = d_rp;
-    d.col_idx = d_ci;
-    d.values = d_va;
-    d.B = d_B;
-    d.ldb = a->Nd;
-    d.C = d_C;
-    d.ldc = a->Nd;
-    d.workspace = d_ws;
-    d.workspace_bytes = align256(ws_bytes);
-    d.status_word = d_status;
-    status = enqueue(&d, st);
-    if (status != CSRSPMM_B200_OK) return fail(status);
-    CUDA_TRY_HOST(cudaMemcpy2DAsync(a->C, (size_t)a->ldc * 4, d_C, (size_t)a->Nd * 4, (size_t)a->Nd * 4,
-                                    (size_t)a->M, cudaMemcpyDeviceToHost, st));
+    for (int k = 0; k < blocks; ++k) {
+        const int32_t r0 = bounds[k], r1 = bounds[k + 1];
+        if (r1 <= r0) continue;
+        const int32_t j0 = a->row_ptr[r0], j1 = a->row_ptr[r1];
+        csrspmm_b200_args d = *a;
+        d.M = r1 - r0;
+        d.nnz = (int64_t)j1 - j0;
+        d.row_ptr = d_rp + r0;
+        d.row_ptr_base = j0;
+        d.col_idx = d_ci + j0;
+        d.values = e2m1 ? static_cast<const void*>(d_va + j0 / 2) : static_cast<const void*>(d_va + (size_t)j0 * 4);
+        d.B = d_B;
+        d.ldb = a->Nd;
+        d.C = d_C + (size_t)r0 * (size_t)a->Nd;
+        d.ldc = a->Nd;
+        d.workspace = d_ws;
+        d.workspace_bytes = align256(ws_bytes);
+        d.status_word = d_status;
+        status = enqueue(&d, st);
+        if (status != CSRSPMM_B200_OK) {
+            cleanup();
+            return status;
+        }
+        cudaStream_t out_stream = st;
+        if (blocks > 1) {
+            CUDA_TRY_HOST(cudaEventRecord(done[k], st));
+            CUDA_TRY_HOST(cudaStreamWaitEvent(copy_stream, done[k], 0));
+            out_stream = copy_stream;
+        }
+        CUDA_TRY_HOST(cudaMemcpy2DAsync(a->C + (size_t)r0 * (size_t)a->ldc, (size_t)a->ldc * 4, d.C, (size_t)a->Nd * 4,
+                                        (size_t)a->Nd * 4, (size_t)(r1 - r0), cudaMemcpyDeviceToHost, out_stream));
+    }
     int word = 0;
     CUDA_TRY_HOST(cudaMemcpyAsync(&word, d_status, 4, cudaMemcpyDeviceToHost, st));
-    if (owned) CUDA_TRY_HOST(cudaFreeAsync(arena, st));
-    owned = false;
     CUDA_TRY_HOST(cudaStreamSynchronize(st));
+    if (copy_stream) CUDA_TRY_HOST(cudaStreamSynchronize(copy_stream));
+    cleanup();
+    if (owned) CUDA_TRY(cudaStreamSynchronize(st));
     if (word & kStatusWaitTimeout) {
         set_last_error("device status word 0x%x: a bounded wait gave up", word);
         return CSRSPMM_B200_ERR_DEVICE_WAIT;

@@ -128,6 +128,7 @@ extern "C" int csrspmm_b200_spmm_noalloc(const csrspmm_b200_args* args, csrspmm_
     p.ncolv = plan.ncolv;
     p.num_items = plan.num_items;
     p.row_ptr = a.row_ptr;
+    p.rp_base = a.row_ptr_base;
     p.col_idx = a.col_idx;
     p.values = a.values;
     p.value_scale = a.value_scale;

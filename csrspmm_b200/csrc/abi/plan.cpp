@@ -40,6 +40,14 @@ int check_args(const csrspmm_b200_args* a, bool need_pointers)
                        a->Nd, (long long)a->nnz);
         return CSRSPMM_B200_ERR_BAD_ARG;
     }
+    if (a->row_ptr_base < 0) {
+        set_last_error("negative row_ptr_base %d", a->row_ptr_base);
+        return CSRSPMM_B200_ERR_BAD_ARG;
+    }
+    if (a->row_ptr_base != 0 && a->value_format == CSRSPMM_B200_VALUES_E2M1 && (a->row_ptr_base & 1)) {
+        set_last_error("row_ptr_base must be even for packed e2m1 values (two codes per byte)");
+        return CSRSPMM_B200_ERR_BAD_ARG;
+    }
     if (a->nnz > 0 && a->Kd == 0) {
         set_last_error("nnz > 0 with Kd == 0");
         return CSRSPMM_B200_ERR_BAD_ARG;

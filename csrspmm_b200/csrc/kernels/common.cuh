@@ -30,6 +30,7 @@ struct SpmmParams {
     int ncolv;            // columns in units of the vector width: ceil(Nd / VW)
     long long num_items;  // M + nnz (merge-path length)
     const int* row_ptr;
+    int rp_base;          // subtracted from every row_ptr entry (row block of a larger matrix)
     const int* col_idx;
     const void* values;
     float value_scale;

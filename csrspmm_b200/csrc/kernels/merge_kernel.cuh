@@ -36,7 +36,7 @@ constexpr int kMergeThreads = 256;
 
 // First i in [max(0, d-nnz), min(d, M)] with row_end[i] > d - i - 1; then j = d - i positions
 // precede the diagonal.  Cooperative over one full warp: 32 probes per round.
-__device__ __forceinline__ int merge_search_warp(long long d, const int* __restrict__ row_end,
+__device__ __forceinline__ int merge_search_warp(long long d, const int* __restrict__ row_end, int rp_base,
                                                  int M, int nnz, int lane)
 {
     int lo = (int)max(0LL, d - (long long)nnz);
@@ -46,7 +46,7 @@ __device__ __forceinline__ int merge_search_warp(long long d, const int* __restr
         const int step = (span + 31) / 32;
         const long long mid = (long long)lo + (long long)lane * step;
         bool pred = false;
-        if (mid < hi) pred = ((long long)__ldg(row_end + mid) <= d - mid - 1);
+        if (mid < hi) pred = ((long long)__ldg(row_end + mid) - rp_base <= d - mid - 1);
         const int t = __popc(__ballot_sync(0xffffffffu, pred));
         if (t == 0) {
             hi = lo;
@@ -109,7 +109,7 @@ __device__ __forceinline__ bool merge_tile_setup(const SpmmParams& p, Smem& s, T
     const long long d1 = min(d0 + (long long)TILE, p.num_items);
     if (warp < 2) {
         const long long d = warp == 0 ? d0 : d1;
-        const int i = merge_search_warp(d, row_end, p.M, p.nnz, tid & 31);
+        const int i = merge_search_warp(d, row_end, p.rp_base, p.M, p.nnz, tid & 31);
         if ((tid & 31) == 0) {
             s.coord[warp * 2] = i;
             s.coord[warp * 2 + 1] = (int)(d - i);
@@ -130,7 +130,7 @@ __device__ __forceinline__ bool merge_tile_setup(const SpmmParams& p, Smem& s, T
 
     // ---- 2. stage the slice ----------------------------------------------------------------
     for (int k = tid; k <= r.nrows; k += kMergeThreads)
-        s.rowend[k] = (k < r.nrows) ? (__ldg(row_end + r.i0 + k) - r.j0) : INT_MAX;
+        s.rowend[k] = (k < r.nrows) ? (__ldg(row_end + r.i0 + k) - p.rp_base - r.j0) : INT_MAX;
     for (int k = tid; k < r.nnzt; k += kMergeThreads) {
         int c = __ldcs(p.col_idx + r.j0 + k);
         if ((unsigned)c >= (unsigned)p.Kd) {  // never fault on a bad index

@@ -33,8 +33,8 @@ __global__ void __launch_bounds__(kRowThreads, row_min_blocks(NV)) spmm_row_kern
     const int row = (int)row_ll;
 
     // clamped so that a malformed row_ptr cannot index outside col_idx/values
-    const int rs = max(__ldg(p.row_ptr + row), 0);
-    const int re = min(__ldg(p.row_ptr + row + 1), p.nnz);
+    const int rs = max(__ldg(p.row_ptr + row) - p.rp_base, 0);
+    const int re = min(__ldg(p.row_ptr + row + 1) - p.rp_base, p.nnz);
     const char* const b_lane = reinterpret_cast<const char*>(p.B) + (size_t)lane * (VW * 4);
     const unsigned long long b_policy = make_b_policy();
 

@@ -98,7 +98,10 @@ typedef struct csrspmm_b200_args {
     int32_t entry;      /* csrspmm_b200_entry */
     int32_t kernel;     /* csrspmm_b200_kernel; AUTO unless pinned */
     int32_t max_row_nnz; /* longest row if known, else 0 (a hint, never trusted for bounds) */
-    int32_t reserved0;
+    int32_t row_ptr_base; /* subtracted from every row_ptr entry; 0 for a whole matrix.  To multiply
+                             rows [r0, r1) of a larger matrix without re-basing its offsets pass
+                             row_ptr + r0, col_idx + row_ptr[r0], values + row_ptr[r0] (F32 values),
+                             M = r1 - r0, nnz = row_ptr[r1] - row_ptr[r0], row_ptr_base = row_ptr[r0] */
     void* workspace;        /* device scratch for the split kernels, or NULL: the library then
                                takes it from the stream-ordered allocator for this call */
     size_t workspace_bytes; /* size of workspace when it is not NULL */

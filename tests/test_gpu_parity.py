@@ -398,3 +398,49 @@ def test_non_default_stream_and_host_round_trip(cuda_lib):
     C_host.fill_(1.0)
     ops.spmm_host(*h, C_host, 2.0, 0.5, arena=arena)
     assert np.allclose(C_host.numpy(), 2.0 * want + 0.5, rtol=RTOL, atol=2e-6)
+
+
+@pytest.mark.parametrize("kernel", KERNELS)
+def test_row_block_of_a_larger_matrix_without_rebasing(cuda_lib, kernel):
+    """args.row_ptr_base: rows [r0, r1) multiplied through offset pointers, row_ptr left as it is."""
+    import ctypes as C
+    p = G.make("cfg3_powerlaw", scale=64, Nd=64)
+    rp, ci, va, B = (dev(x) for x in arrays(p))
+    whole = ops.spmm(rp, ci, va, B, kernel=kernel, sync=True)
+    out = torch.full((p.M, p.Nd), float("nan"), device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    ws = torch.empty(ops.workspace_bytes(p.M, p.Kd, p.Nd, p.nnz), dtype=torch.uint8, device="cuda")
+    cuts = [0, 1, 5000, 5000, p.M // 2 + 3, p.M]  # includes an empty block and a one-row block
+    for r0, r1 in zip(cuts[:-1], cuts[1:]):
+        j0, j1 = int(p.row_ptr[r0]), int(p.row_ptr[r1])
+        a = _lib.make_args(r1 - r0, p.Kd, p.Nd, j1 - j0, rp.data_ptr() + 4 * r0, ci.data_ptr() + 4 * j0,
+                           va.data_ptr() + 4 * j0, B.data_ptr(), out.data_ptr() + 4 * r0 * p.Nd,
+                           kernel=_lib.KERNEL_IDS[kernel], row_ptr_base=j0, workspace=ws.data_ptr(),
+                           workspace_bytes=ws.numel(), status_word=status.data_ptr())
+        assert cuda_lib.csrspmm_b200_spmm_sync(C.byref(a), None) == _lib.OK, cuda_lib.csrspmm_b200_last_error()
+    assert int(status.item()) == 0
+    # row blocks cut the merge path at other places than the whole product: same values up to re-association
+    assert torch.allclose(out, whole, rtol=1e-4, atol=1e-5)
+    if kernel == "row":
+        assert torch.equal(out, whole)
+
+
+def test_host_round_trip_in_row_blocks(cuda_lib):
+    """csrspmm_b200_spmm_host on a C large enough (>= 64 MiB) to be computed and copied back in row blocks."""
+    p = G.make("cfg3_powerlaw", scale=8, Nd=128)
+    assert p.M * p.Nd * 4 >= 64 << 20
+    h = [torch.from_numpy(x).pin_memory() for x in arrays(p)]
+    C_host = torch.empty(p.M, p.Nd).pin_memory()
+    ops.spmm_host(*h, C_host)
+    f64, mag = oracle.spmm_f64(p.row_ptr, p.col_idx, p.values, p.B, threads=4)
+    got = C_host.numpy()
+    assert (np.abs(got - f64) <= RTOL * mag + ATOL).all()
+    # row blocks cut the merge path elsewhere than a whole-matrix call: same sums, other association
+    dev_result = ops.spmm(*(x.cuda() for x in h), kernel="merge", sync=True).cpu().numpy()
+    assert (np.abs(got - dev_result) <= 2 * (RTOL * mag + ATOL)).all()
+    # beta != 0 through the blocked path
+    C0 = np.full((p.M, p.Nd), 2.0, np.float32)
+    C_host.copy_(torch.from_numpy(C0))
+    ops.spmm_host(*h, C_host, 1.0, 0.5)
+    f64b, magb = oracle.spmm_f64(p.row_ptr, p.col_idx, p.values, p.B, C0, 1.0, 0.5, threads=4)
+    assert (np.abs(C_host.numpy() - f64b) <= RTOL * magb + ATOL).all()
