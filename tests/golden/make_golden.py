@@ -1,6 +1,7 @@
 """Generates tests/golden/*.npz from the REFERENCE's own host code.
 
-Run in a container that has the reference checkout (default /root/reference):
+Run where a checkout of the reference is available (its location: the CSRSPMM_REFERENCE
+environment variable or the REFERENCE variable of oracle/Makefile):
 
     make -C oracle ref && python tests/golden/make_golden.py
 
