@@ -193,7 +193,7 @@ int make_plan(const csrspmm_b200_args* a, Plan* plan)
         if (kernel == CSRSPMM_B200_KERNEL_MERGE) {
             fill_split_geometry(a, plan, (256 / plan->G) * kShapes[plan->shape].TG);
         } else {
-            const int groups = 256 / plan->G;
+            const int groups = CSRSPMM_TUNE_ROW_THREADS / plan->G;
             plan->grid = ((long long)a->M + groups - 1) / groups;
         }
     }

@@ -19,7 +19,7 @@ namespace csrspmm_b200 {
 
 namespace cg = cooperative_groups;
 
-constexpr int kRowThreads = 256;
+constexpr int kRowThreads = CSRSPMM_TUNE_ROW_THREADS;
 
 // FULL: one pass covers the row exactly (G * NV == ncolv), so no column guard is compiled in.
 template <int G, int NV, int VW, int U, int FMT, bool FULL>
@@ -56,18 +56,27 @@ __global__ void __launch_bounds__(kRowThreads, row_min_blocks(NV)) spmm_row_kern
             }
         };
 
-        for (int base = rs; base < re; base += G) {
-            const int jj = base + lane;
-            int c_l = 0;
-            float a_l = 0.f;
+        // (col, val) of the row, G at a time: the next chunk is requested before the current one is
+        // consumed, so its latency overlaps the multiply-adds
+        auto load_pair = [&](int jj, int& c, float& a) {
+            c = 0;
+            a = 0.f;
             if (jj < re) {
-                c_l = __ldcs(p.col_idx + jj);
-                a_l = load_value<FMT>(p.values, jj, p.value_scale);
-                if ((unsigned)c_l >= (unsigned)p.Kd) {  // never fault on a bad index
-                    c_l = min(max(c_l, 0), p.Kd - 1);
+                c = __ldcs(p.col_idx + jj);
+                a = load_value<FMT>(p.values, jj, p.value_scale);
+                if ((unsigned)c >= (unsigned)p.Kd) {  // never fault on a bad index
+                    c = min(max(c, 0), p.Kd - 1);
                     report_status(p, kStatusColClamped);
                 }
             }
+        };
+        int c_next;
+        float a_next;
+        load_pair(rs + lane, c_next, a_next);
+        for (int base = rs; base < re; base += G) {
+            const int c_l = c_next;
+            const float a_l = a_next;
+            load_pair(base + G + lane, c_next, a_next);
             const int n = min(G, re - base);
             int t = 0;
             for (; t + U <= n; t += U) {  // whole batches: no per-element test

@@ -46,6 +46,12 @@
 #define CSRSPMM_TUNE_TMA_MINB 2
 #endif
 
+// threads per CTA of the row kernel (128: 4 rows per CTA at G = 32; small CTAs keep the tail short
+// when there are only a few thousand rows -- 4096 rows in 256-thread CTAs left a 15 % imbalance)
+#ifndef CSRSPMM_TUNE_ROW_THREADS
+#define CSRSPMM_TUNE_ROW_THREADS 128
+#endif
+
 // minimum resident CTAs per SM requested from the compiler (caps registers per thread)
 #ifndef CSRSPMM_TUNE_MERGE_MINB_NV1
 #define CSRSPMM_TUNE_MERGE_MINB_NV1 4
@@ -57,13 +63,13 @@
 #define CSRSPMM_TUNE_MERGE_MINB_NV4 2
 #endif
 #ifndef CSRSPMM_TUNE_ROW_MINB_NV1
-#define CSRSPMM_TUNE_ROW_MINB_NV1 4
+#define CSRSPMM_TUNE_ROW_MINB_NV1 8
 #endif
 #ifndef CSRSPMM_TUNE_ROW_MINB_NV2
-#define CSRSPMM_TUNE_ROW_MINB_NV2 4
+#define CSRSPMM_TUNE_ROW_MINB_NV2 8
 #endif
 #ifndef CSRSPMM_TUNE_ROW_MINB_NV4
-#define CSRSPMM_TUNE_ROW_MINB_NV4 2
+#define CSRSPMM_TUNE_ROW_MINB_NV4 4
 #endif
 
 // lane-group shapes by dense width class k (column vectors per row <= 8, 16, 32, 64, more):

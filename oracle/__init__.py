@@ -20,6 +20,7 @@ import numpy as np
 _HERE = Path(__file__).resolve().parent
 _LIB_PATH = _HERE / "_build" / "libspmm_oracle.so"
 _REF_PATH = _HERE / "_ref" / "libcsrspmm_ref_host.so"
+_REF_GPU_PATH = _HERE / "_ref" / "libcsrspmm_ref_gpu.so"
 
 _i32p = C.POINTER(C.c_int32)
 _f32p = C.POINTER(C.c_float)
@@ -35,6 +36,7 @@ def build(with_ref: bool | None = None) -> None:
         with_ref = Path(ref_root, "src", "host", "dense_utils.cpp").exists()
     if with_ref:
         targets.append("ref")
+        targets.append("refgpu")
         if (_HERE.parent / "csrspmm_b200" / "lib" / "libcsrspmm_b200.so").exists():
             targets.append("dropin")
     subprocess.run(["make", "-s", "-C", str(_HERE), f"REFERENCE={ref_root}", *targets], check=True)
@@ -263,3 +265,29 @@ class Reference:
 
     def compression_ratio(self, H, W, nnz) -> float:
         return float(self.L.ref_compression_ratio(H, W, nnz))
+
+
+class ReferenceGpu:
+    """The reference's own GPU kernels (recompiled for sm_100a, oracle/_ref/libcsrspmm_ref_gpu.so),
+    launched on torch CUDA tensors through oracle/ref_gpu_shim.cu.  Legacy default stream."""
+
+    ALGOS = {"Naive": 0, "WarpPerRow": 2, "WarpPerRowFp4": 3, "WarpPerRowSmem": 4, "WarpPerRowSmemFp4": 5}
+
+    def __init__(self):
+        if not _REF_GPU_PATH.exists():
+            raise FileNotFoundError(f"{_REF_GPU_PATH} not built (needs the reference checkout: make -C oracle refgpu)")
+        self.L = C.CDLL(str(_REF_GPU_PATH))
+        self.L.ref_gpu_spmm.argtypes = [C.c_int] * 5 + [C.c_void_p] * 3 + [C.c_int] + [C.c_void_p] * 2 + [C.c_float] * 2
+        self.L.ref_gpu_spmm.restype = C.c_int
+
+    @staticmethod
+    def available() -> bool:
+        return _REF_GPU_PATH.exists()
+
+    def spmm(self, algo, row_ptr, col_idx, values, B, C_out, alpha=1.0, beta=0.0, max_row_nnz=0) -> int:
+        """Enqueue C_out = alpha*A*B + beta*C_out with the reference kernel `algo`.  Returns 0, or -2
+        when the reference cannot run this shape (32-bit offsets, shared memory, alignment)."""
+        M, Kd, Nd = row_ptr.numel() - 1, B.shape[0], B.shape[1]
+        return int(self.L.ref_gpu_spmm(self.ALGOS[algo], M, Kd, Nd, col_idx.numel(), row_ptr.data_ptr(),
+                                       col_idx.data_ptr(), values.data_ptr(), int(max_row_nnz), B.data_ptr(),
+                                       C_out.data_ptr(), float(alpha), float(beta)))
