@@ -35,10 +35,20 @@ void launch_row(const SpmmParams& p, const Plan& plan, cudaStream_t st)
 {
     constexpr int G = kShapes[S].G, NV = kShapes[S].NV;
     constexpr int U = VW == 1 ? 8 : row_unroll(NV);
-    if (VW == 4 && plan.full)
-        spmm_row_kernel<G, NV, VW, U, FMT, (VW == 4)><<<(unsigned)plan.grid, kRowThreads, 0, st>>>(p);
-    else
-        spmm_row_kernel<G, NV, VW, U, FMT, false><<<(unsigned)plan.grid, kRowThreads, 0, st>>>(p);
+    constexpr int ULOW = VW == 1 ? 8 : row_unroll_low(NV);
+    constexpr int MINB = row_min_blocks(NV);
+    const unsigned grid = (unsigned)plan.grid;
+    if (VW == 4 && plan.full) {
+        if (plan.low_occupancy && ULOW != U)
+            spmm_row_kernel<G, NV, VW, ULOW, FMT, (VW == 4), 2><<<grid, kRowThreads, 0, st>>>(p);
+        else
+            spmm_row_kernel<G, NV, VW, U, FMT, (VW == 4), MINB><<<grid, kRowThreads, 0, st>>>(p);
+    } else {
+        if (plan.low_occupancy && ULOW != U)
+            spmm_row_kernel<G, NV, VW, ULOW, FMT, false, 2><<<grid, kRowThreads, 0, st>>>(p);
+        else
+            spmm_row_kernel<G, NV, VW, U, FMT, false, MINB><<<grid, kRowThreads, 0, st>>>(p);
+    }
 }
 
 template <int S, int VW, int FMT>

@@ -155,11 +155,7 @@ int make_plan(const csrspmm_b200_args* a, Plan* plan)
         const double avg = a->M > 0 ? (double)a->nnz / (double)a->M : 0.0;
         const double row_limit = avg * 4.0 > 64.0 ? avg * 4.0 : 64.0;
         const double b_bytes = (double)a->Kd * (double)a->Nd * 4.0;
-        // ... unless there are too few rows to fill 148 SMs with whole-row work while the rows are
-        // long enough to split (measured on the reference's sweep shapes: with 512-1024 rows of
-        // 200-600 non-zeros the merge kernel is 10-45 % ahead; from 4096 rows on the row kernel wins)
-        const bool few_long_rows = a->M < 2048 && avg >= 192.0;
-        const bool rows_even = a->max_row_nnz > 0 && (double)a->max_row_nnz <= row_limit && !few_long_rows;
+        const bool rows_even = a->max_row_nnz > 0 && (double)a->max_row_nnz <= row_limit;
         if (tma_can_run(a) && a->Nd > 384 && b_bytes >= 1073741824.0 && !rows_even)
             kernel = CSRSPMM_B200_KERNEL_TMA;
         else if (rows_even)
@@ -195,6 +191,7 @@ int make_plan(const csrspmm_b200_args* a, Plan* plan)
         } else {
             const int groups = CSRSPMM_TUNE_ROW_THREADS / plan->G;
             plan->grid = ((long long)a->M + groups - 1) / groups;
+            plan->low_occupancy = (long long)a->M * plan->G / 32 < 148LL * 8;
         }
     }
     if (plan->grid > 0x7fffffffLL) {

@@ -16,6 +16,7 @@ namespace csrspmm_b200 {
 struct Plan {
     int kernel = CSRSPMM_B200_KERNEL_ROW;  // resolved, never AUTO
     int shape = 0;                         // index into kShapes (tuning.h)
+    bool low_occupancy = false;            // row kernel: fewer than 8 warps of rows per SM
     bool full = false;                     // one pass covers the row exactly: G*NV == ncolv
     int G = 8, NV = 1, VW = 4;             // lanes per group, vectors per lane, vector width
     int ncolv = 0;                         // ceil(Nd / VW)

@@ -22,8 +22,9 @@ namespace cg = cooperative_groups;
 constexpr int kRowThreads = CSRSPMM_TUNE_ROW_THREADS;
 
 // FULL: one pass covers the row exactly (G * NV == ncolv), so no column guard is compiled in.
-template <int G, int NV, int VW, int U, int FMT, bool FULL>
-__global__ void __launch_bounds__(kRowThreads, row_min_blocks(NV)) spmm_row_kernel(const SpmmParams p)
+// MINB: resident CTAs per SM asked of the compiler (caps the registers).
+template <int G, int NV, int VW, int U, int FMT, bool FULL, int MINB>
+__global__ void __launch_bounds__(kRowThreads, MINB) spmm_row_kernel(const SpmmParams p)
 {
     constexpr int GROUPS = kRowThreads / G;
     const cg::thread_block_tile<G> tile = cg::tiled_partition<G>(cg::this_thread_block());
@@ -37,6 +38,10 @@ __global__ void __launch_bounds__(kRowThreads, row_min_blocks(NV)) spmm_row_kern
     const int re = min(__ldg(p.row_ptr + row + 1) - p.rp_base, p.nnz);
     const char* const b_lane = reinterpret_cast<const char*>(p.B) + (size_t)lane * (VW * 4);
     const unsigned long long b_policy = make_b_policy();
+#if CSRSPMM_TUNE_ROW_STAGE_SMEM
+    __shared__ int2 s_cv[kRowThreads];  // each group's current chunk of (col, val bits)
+    int2* const my_cv = s_cv + (threadIdx.x / G) * G;
+#endif
 
     for (int cb = 0; cb < p.ncolv; cb += G * NV) {
         const char* const b_pass = b_lane + (size_t)cb * (VW * 4);
@@ -74,18 +79,28 @@ __global__ void __launch_bounds__(kRowThreads, row_min_blocks(NV)) spmm_row_kern
         float a_next;
         load_pair(rs + lane, c_next, a_next);
         for (int base = rs; base < re; base += G) {
+#if CSRSPMM_TUNE_ROW_STAGE_SMEM
+            tile.sync();  // the previous chunk has been consumed by every lane of the group
+            my_cv[lane] = make_int2(c_next, __float_as_int(a_next));
+            tile.sync();
+#define ROW_COL(k) (my_cv[(k)].x)
+#define ROW_VAL(k) (__int_as_float(my_cv[(k)].y))
+#else
             const int c_l = c_next;
             const float a_l = a_next;
+#define ROW_COL(k) (tile.shfl(c_l, (k)))
+#define ROW_VAL(k) (tile.shfl(a_l, (k)))
+#endif
             load_pair(base + G + lane, c_next, a_next);
             const int n = min(G, re - base);
             int t = 0;
             for (; t + U <= n; t += U) {  // whole batches: no per-element test
                 Vec<VW> bq[U][NV];
 #pragma unroll
-                for (int u = 0; u < U; ++u) load_b(bq[u], tile.shfl(c_l, t + u));
+                for (int u = 0; u < U; ++u) load_b(bq[u], ROW_COL(t + u));
 #pragma unroll
                 for (int u = 0; u < U; ++u) {
-                    const float a = tile.shfl(a_l, t + u);
+                    const float a = ROW_VAL(t + u);
 #pragma unroll
                     for (int v = 0; v < NV; ++v) acc[v].fma(a, bq[u][v]);
                 }
@@ -94,16 +109,18 @@ __global__ void __launch_bounds__(kRowThreads, row_min_blocks(NV)) spmm_row_kern
                 Vec<VW> bq[U][NV];
 #pragma unroll
                 for (int u = 0; u < U; ++u)
-                    if (t + u < n) load_b(bq[u], tile.shfl(c_l, t + u));
+                    if (t + u < n) load_b(bq[u], ROW_COL(t + u));
 #pragma unroll
                 for (int u = 0; u < U; ++u) {
                     if (t + u < n) {
-                        const float a = tile.shfl(a_l, t + u);
+                        const float a = ROW_VAL(t + u);
 #pragma unroll
                         for (int v = 0; v < NV; ++v) acc[v].fma(a, bq[u][v]);
                     }
                 }
             }
+#undef ROW_COL
+#undef ROW_VAL
         }
         store_row<G, NV, VW>(p, row, cb, lane, acc);
     }

@@ -46,10 +46,28 @@
 #define CSRSPMM_TUNE_TMA_MINB 2
 #endif
 
+// row kernel: how a group hands its G loaded (col, val) pairs to all its lanes: 1 = through a
+// shared-memory slice (broadcast reads), 0 = lane to lane by shuffle
+#ifndef CSRSPMM_TUNE_ROW_STAGE_SMEM
+#define CSRSPMM_TUNE_ROW_STAGE_SMEM 1
+#endif
+
 // threads per CTA of the row kernel (128: 4 rows per CTA at G = 32; small CTAs keep the tail short
 // when there are only a few thousand rows -- 4096 rows in 256-thread CTAs left a 15 % imbalance)
 #ifndef CSRSPMM_TUNE_ROW_THREADS
 #define CSRSPMM_TUNE_ROW_THREADS 128
+#endif
+
+// row kernel, few rows (fewer warps of work than 8 per SM): registers are plentiful and latency is
+// everything, so many more loads are kept in flight per lane
+#ifndef CSRSPMM_TUNE_ROW_ULOW_NV1
+#define CSRSPMM_TUNE_ROW_ULOW_NV1 16
+#endif
+#ifndef CSRSPMM_TUNE_ROW_ULOW_NV2
+#define CSRSPMM_TUNE_ROW_ULOW_NV2 8
+#endif
+#ifndef CSRSPMM_TUNE_ROW_ULOW_NV4
+#define CSRSPMM_TUNE_ROW_ULOW_NV4 4
 #endif
 
 // minimum resident CTAs per SM requested from the compiler (caps registers per thread)
@@ -133,6 +151,7 @@ constexpr ShapeDesc kShapes[kNumShapes] = {
 
 constexpr int merge_unroll(int nv) { return nv == 1 ? CSRSPMM_TUNE_MERGE_U_NV1 : (nv == 2 ? CSRSPMM_TUNE_MERGE_U_NV2 : CSRSPMM_TUNE_MERGE_U_NV4); }
 constexpr int row_unroll(int nv) { return nv == 1 ? CSRSPMM_TUNE_ROW_U_NV1 : (nv == 2 ? CSRSPMM_TUNE_ROW_U_NV2 : CSRSPMM_TUNE_ROW_U_NV4); }
+constexpr int row_unroll_low(int nv) { return nv == 1 ? CSRSPMM_TUNE_ROW_ULOW_NV1 : (nv == 2 ? CSRSPMM_TUNE_ROW_ULOW_NV2 : CSRSPMM_TUNE_ROW_ULOW_NV4); }
 constexpr int row_min_blocks(int nv) { return nv == 1 ? CSRSPMM_TUNE_ROW_MINB_NV1 : (nv == 2 ? CSRSPMM_TUNE_ROW_MINB_NV2 : CSRSPMM_TUNE_ROW_MINB_NV4); }
 constexpr int merge_min_blocks(int nv) { return nv == 1 ? CSRSPMM_TUNE_MERGE_MINB_NV1 : (nv == 2 ? CSRSPMM_TUNE_MERGE_MINB_NV2 : CSRSPMM_TUNE_MERGE_MINB_NV4); }
 

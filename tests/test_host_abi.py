@@ -70,8 +70,8 @@ def test_kernel_selection():
     sel = ops.selected_kernel
     # short even rows with a trustworthy max_row_nnz -> row kernel
     assert sel(16384, 16384, 128, 268000, max_row_nnz=38) == "row"
-    # few but long rows: whole-row work cannot fill the chip -> merge-path
-    assert sel(1024, 2048, 128, 419_517, max_row_nnz=470) == "merge"
+    # few rows: still the row kernel (its deep-unroll variant for an underfilled chip)
+    assert sel(1024, 2048, 128, 419_517, max_row_nnz=470) == "row"
     assert sel(512, 1024, 64, 52_205, max_row_nnz=140) == "row"
     assert sel(4096, 4096, 128, 3_356_995, max_row_nnz=900) == "row"
     # unknown or skewed row lengths -> merge-path
