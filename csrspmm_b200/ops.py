@@ -184,8 +184,28 @@ def selected_kernel(M, Kd, Nd, nnz, *, entry="naive", max_row_nnz=0, kernel="aut
 # (torch_csrspmm/torch_csrspmm_naive.cpp:32-34); the product with zero is skipped here, which
 # changes nothing but the sign of an exact zero.
 
+_ROW_STATS_CACHE: dict = {}
+
+
+def _longest_row_hint(row_ptr) -> int:
+    """Longest row of the matrix behind this row_ptr tensor, measured once (one small kernel and a
+    host read) and remembered per (address, length, version).  It only steers the kernel choice, so
+    a stale entry -- another matrix later placed at the same address -- costs speed, never
+    correctness."""
+    key = (row_ptr.data_ptr(), row_ptr.numel(), row_ptr._version, row_ptr.device.index)
+    hit = _ROW_STATS_CACHE.get(key)
+    if hit is None:
+        if len(_ROW_STATS_CACHE) >= 64:
+            _ROW_STATS_CACHE.pop(next(iter(_ROW_STATS_CACHE)))
+        hit = row_stats(row_ptr)["max_row_nnz"] if row_ptr.numel() > 1 else 0
+        _ROW_STATS_CACHE[key] = hit
+    return hit
+
+
 def _op(entry, row_ptr, col_idx, values, B, alpha, beta, max_row_nnz=0):
     del beta
+    if int(max_row_nnz) <= 0 and row_ptr.is_cuda and row_ptr.dtype == torch.int32:
+        max_row_nnz = _longest_row_hint(row_ptr)  # the reference's non-smem ops carry no such argument
     return spmm(row_ptr, col_idx, values, B, None, float(alpha), 0.0, entry=entry, max_row_nnz=int(max_row_nnz))
 
 
