@@ -7,6 +7,7 @@
 #include <cuda_runtime.h>
 
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 
 #include "../kernels/aux_kernels.cuh"
@@ -108,11 +109,28 @@ cudaError_t dispatch_tma(const SpmmParams& p, const Plan& plan, cudaStream_t st)
     }
 }
 
+// CSRSPMM_VALIDATE=1 in the environment: check the CSR structure on the device before every
+// product (costs a kernel and a stream synchronisation; off by default).
+bool validation_requested()
+{
+    static const bool on = [] {
+        const char* e = std::getenv("CSRSPMM_VALIDATE");
+        return e != nullptr && *e != 0 && *e != '0';
+    }();
+    return on;
+}
+
 int enqueue(const csrspmm_b200_args* a, cudaStream_t st)
 {
     int status = check_args(a, true);
     if (status != CSRSPMM_B200_OK) return status;
     if (a->M == 0 || a->Nd == 0) return CSRSPMM_B200_OK;
+    if (validation_requested() && a->row_ptr_base == 0) {
+        uint32_t problems = 0;
+        status = csrspmm_b200_validate_csr_device(a->M, a->Kd, a->nnz, a->row_ptr, a->col_idx, &problems,
+                                                  reinterpret_cast<csrspmm_b200_stream_t>(st));
+        if (status != CSRSPMM_B200_OK) return status;
+    }
 
     Plan plan;
     status = make_plan(a, &plan);

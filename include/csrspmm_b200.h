@@ -113,7 +113,9 @@ const char* csrspmm_b200_status_string(int status);
 /* Text of the most recent failure on the calling thread ("" if none). */
 const char* csrspmm_b200_last_error(void);
 
-/* Asynchronous: enqueue the SpMM on `stream` and return.  Device pointers. */
+/* Asynchronous: enqueue the SpMM on `stream` and return.  Device pointers.  With CSRSPMM_VALIDATE=1
+ * in the environment the CSR structure is first checked on the device (one extra kernel and a
+ * stream synchronisation) and a malformed matrix is refused with ERR_INVALID_CSR. */
 int csrspmm_b200_spmm(const csrspmm_b200_args* args, csrspmm_b200_stream_t stream);
 
 /* As above, then wait for the stream and report launch/execution errors and the status word. */

@@ -444,3 +444,65 @@ def test_host_round_trip_in_row_blocks(cuda_lib):
     ops.spmm_host(*h, C_host, 1.0, 0.5)
     f64b, magb = oracle.spmm_f64(p.row_ptr, p.col_idx, p.values, p.B, C0, 1.0, 0.5, threads=4)
     assert (np.abs(C_host.numpy() - f64b) <= RTOL * magb + ATOL).all()
+
+
+def test_randomised_shapes_all_kernels(cuda_lib):
+    """Forty seeded random problems: odd sizes, empty and very long rows, unsorted and repeated
+    column indices (the kernels, like the reference's, take stored order as it comes)."""
+    rng = np.random.default_rng(2024)
+    for case in range(40):
+        M, Kd = int(rng.integers(1, 3000)), int(rng.integers(1, 3000))
+        Nd = int(rng.choice([1, 3, 4, 8, 20, 31, 32, 64, 96, 128, 200, 256, 384, 512, 600]))
+        kind = case % 4
+        if kind == 0:
+            lens = rng.binomial(Kd, min(8.0 / Kd, 0.5), M)
+        elif kind == 1:
+            lens = np.clip(np.rint(rng.zipf(1.8, M) * 2.0), 0, Kd // 2 + 1).astype(np.int64)
+        elif kind == 2:
+            lens = np.where(rng.random(M) < 0.7, 0, rng.integers(0, min(Kd, 40) + 1, M))
+        else:
+            lens = np.full(M, min(Kd, int(rng.integers(1, 70))))
+        p = G.random_csr(M, Kd, Nd, 0.0, seed=1000 + case, lengths=lens)
+        ci = p.col_idx.copy()
+        if case % 3 == 0 and p.nnz > 4:  # shuffle inside rows and plant repeats
+            for r in rng.integers(0, M, 20):
+                s, e = p.row_ptr[r], p.row_ptr[r + 1]
+                if e - s > 1:
+                    rng.shuffle(ci[s:e])
+                    ci[s] = ci[e - 1]
+        alpha, beta = float(rng.choice([1.0, -0.5, 2.25])), float(rng.choice([0.0, 0.0, 1.0, -1.5]))
+        C0 = rng.standard_normal((M, Nd), dtype=np.float32)
+        a = (p.row_ptr, ci, p.values, p.B)
+        for kernel in KERNELS:
+            if kernel == "tma" and not tma_ok(Nd):
+                continue
+            got = run(a, kernel, C0, alpha, beta)
+            if kernel == "row":
+                want = oracle.spmm(*a, C0, alpha, beta, threads=4)
+                assert np.array_equal(got, want), f"case {case} {M}x{Kd}x{Nd}"
+            else:
+                f64, mag = oracle.spmm_f64(*a, C0, alpha, beta, threads=4)
+                assert (np.abs(got - f64) <= RTOL * mag + ATOL).all(), f"case {case} {kernel} {M}x{Kd}x{Nd}"
+
+
+def test_validation_through_the_environment(cuda_lib):
+    """CSRSPMM_VALIDATE=1 makes every product check its matrix first (read at first use, so a child process)."""
+    import subprocess
+    import sys
+    code = """
+import numpy as np, torch, sys
+sys.path.insert(0, %r)
+from csrspmm_b200 import _lib, generators as G, ops
+p = G.random_csr(50, 40, 16, 0.2, seed=1)
+t = [torch.from_numpy(x).cuda() for x in (p.row_ptr, p.col_idx, p.values, p.B)]
+ops.spmm(*t, sync=True)
+bad = p.row_ptr.copy(); bad[10], bad[11] = bad[11], bad[10] - 1
+try:
+    ops.spmm(torch.from_numpy(bad).cuda(), *t[1:], sync=True)
+except _lib.SpmmError as e:
+    assert e.status == _lib.ERR_INVALID_CSR
+    print("refused")
+""" % str(Path(__file__).resolve().parents[1])
+    env = dict(__import__("os").environ, CSRSPMM_VALIDATE="1")
+    out = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, env=env, timeout=300)
+    assert out.returncode == 0 and "refused" in out.stdout, out.stdout + out.stderr
