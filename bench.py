@@ -419,7 +419,7 @@ def main(argv=None):
     if not ns.no_extras:
         keep_rows = torch.arange(0, my_rows, max(my_rows // 4096, 1), device=dev)
         keep_vals = C_out[keep_rows].clone()  # the device-timed result on a row sample, to compare e2e against
-        if world == 1:
+        if world == 1 or Kd % world != 0:  # (an uneven split of B's rows: every rank uploads all of B itself)
             h = {k: torch.empty(v.shape, dtype=v.dtype, pin_memory=True) for k, v in t.items()}
             for k in h:
                 h[k].copy_(t[k])
@@ -455,7 +455,7 @@ def main(argv=None):
         torch.cuda.synchronize()
         e2e_sec = (time.perf_counter() - t0) / ns.e2e_steps
         e2e_sec = D.max_over_ranks(e2e_sec, dev)
-        C_e2e = C_host if world == 1 else runner.C_host
+        C_e2e = C_host if (world == 1 or Kd % world != 0) else runner.C_host
         # same product as the device-timed run (row blocks may associate split rows differently)
         same = bool(torch.allclose(C_e2e[keep_rows.cpu()], keep_vals.cpu(), rtol=1e-3, atol=1e-3))
         same = D.sum_over_ranks(0.0 if same else 1.0, dev) == 0.0
