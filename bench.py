@@ -51,7 +51,7 @@ NCU_TRAFFIC = {
     ("cfg5_xl", "tma"): (32.88e9, 16777248),           # 1/8 of the rows, profiles/tma_and_merge_kernel_cfg5_xl_eighth.md
     ("cfg5_xl", "merge"): (32.96e9, 16777248),         # 1/8 of the rows, same file
     ("cfg2_medium", "row"): (10.6e6, 268783),          # profiles/row_kernel_cfg2_medium_and_cfg4.md
-    ("cfg4_fp4", "row"): (1.412e9, 21471764),          # same file
+    ("cfg4_fp4", "row"): (0.977e9, 21471764),          # same file
 }
 
 

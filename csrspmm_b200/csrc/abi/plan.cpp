@@ -192,6 +192,13 @@ int make_plan(const csrspmm_b200_args* a, Plan* plan)
             const int groups = CSRSPMM_TUNE_ROW_THREADS / plan->G;
             plan->grid = ((long long)a->M + groups - 1) / groups;
             plan->low_occupancy = (long long)a->M * plan->G / 32 < 148LL * 8;
+#if CSRSPMM_TUNE_ROW_PERSISTENT > 0
+            // many short rows: a CTA that lives for four 16-entry rows costs more to start than to
+            // run (cfg2: 20.5 -> 18.6 us; 65536 rows of 13: 53 -> 45 us; long rows prefer the
+            // finer dynamic balance of one CTA per few rows)
+            if (a->nnz <= 64 * (long long)a->M && plan->grid > 148LL * CSRSPMM_TUNE_ROW_PERSISTENT)
+                plan->grid = 148LL * CSRSPMM_TUNE_ROW_PERSISTENT;
+#endif
         }
     }
     if (plan->grid > 0x7fffffffLL) {

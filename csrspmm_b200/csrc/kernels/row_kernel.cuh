@@ -29,8 +29,10 @@ __global__ void __launch_bounds__(kRowThreads, MINB) spmm_row_kernel(const SpmmP
     constexpr int GROUPS = kRowThreads / G;
     const cg::thread_block_tile<G> tile = cg::tiled_partition<G>(cg::this_thread_block());
     const int lane = tile.thread_rank();
-    const long long row_ll = (long long)blockIdx.x * GROUPS + (threadIdx.x / G);
-    if (row_ll >= p.M) return;
+    // rows are dealt to the groups of the grid round-robin; with one CTA per GROUPS rows (the
+    // default grid) every group gets exactly one row
+    const long long group_stride = (long long)gridDim.x * GROUPS;
+    for (long long row_ll = (long long)blockIdx.x * GROUPS + (threadIdx.x / G); row_ll < p.M; row_ll += group_stride) {
     const int row = (int)row_ll;
 
     // clamped so that a malformed row_ptr cannot index outside col_idx/values
@@ -123,6 +125,7 @@ __global__ void __launch_bounds__(kRowThreads, MINB) spmm_row_kernel(const SpmmP
 #undef ROW_VAL
         }
         store_row<G, NV, VW>(p, row, cb, lane, acc);
+    }
     }
 }
 

@@ -52,6 +52,12 @@
 #define CSRSPMM_TUNE_ROW_STAGE_SMEM 1
 #endif
 
+// row kernel on short rows (mean of 64 non-zeros or fewer): at most this many CTAs per SM, each
+// looping over rows, instead of one short-lived CTA per 128/G rows (0 = never)
+#ifndef CSRSPMM_TUNE_ROW_PERSISTENT
+#define CSRSPMM_TUNE_ROW_PERSISTENT 8
+#endif
+
 // threads per CTA of the row kernel (128: 4 rows per CTA at G = 32; small CTAs keep the tail short
 // when there are only a few thousand rows -- 4096 rows in 256-thread CTAs left a 15 % imbalance)
 #ifndef CSRSPMM_TUNE_ROW_THREADS
