@@ -238,7 +238,7 @@ def cusparse_summary(res, flops):
             "all_us": {k: (round(v * 1e6, 1) if isinstance(v, float) else v) for k, v in res.items()}}
 
 
-def cpu_sample(torch, G, oracle, prob, sample_rows, threads, repeats=2):
+def cpu_sample(torch, G, oracle, prob, sample_rows, threads, repeats=3):
     """Times the CPU oracle on rows [0, sample_rows) of the problem (B complete, on the host)."""
     rp = prob.row_ptr[: sample_rows + 1]
     rp_h = (rp.cpu().numpy() if hasattr(rp, "cpu") else np.asarray(rp)).astype(np.int32)
@@ -246,17 +246,21 @@ def cpu_sample(torch, G, oracle, prob, sample_rows, threads, repeats=2):
     to_h = (lambda x: x.cpu().numpy()) if hasattr(prob.col_idx, "cpu") else np.asarray
     ci_h, va_h = to_h(prob.col_idx[:n]), to_h(prob.values[:n])
     B_h = to_h(prob.B)
+    C_h = np.zeros((sample_rows, prob.Nd), np.float32)
+    oracle.spmm(rp_h, ci_h, va_h, B_h, threads=threads, out=C_h)  # untimed: pages in C, warms the caches
     best = float("inf")
     for _ in range(repeats):
         t0 = time.perf_counter()
-        oracle.spmm(rp_h, ci_h, va_h, B_h, threads=threads)
+        oracle.spmm(rp_h, ci_h, va_h, B_h, threads=threads, out=C_h)
         best = min(best, time.perf_counter() - t0)
     return 2.0 * n * prob.Nd / best / 1e9, n, best
 
 
 def sample_rows_for(name, M):
-    # sized for roughly 10-30 s of CPU work on a few dozen cores
-    return {"cfg5_xl": M // 16, "cfg3_powerlaw": M // 2, "cfg4_fp4": M // 4}.get(name, M)
+    """Rows of the workload the CPU legs run.  All of them: even config 5 (137 GFLOP, 275 GB of
+    gathered rows) is a few seconds per pass on the host cores, so no sub-sampling is needed to
+    stay within the time bound; the three timed passes add up to about ten seconds of CPU work."""
+    return M
 
 
 # ---------------------------------------------------------------------------------------------------
@@ -278,10 +282,11 @@ def run_reference_arm(ns):
     n = int(rp_h[-1])
     to_h = (lambda x: x.cpu().numpy()) if hasattr(prob.col_idx, "cpu") else np.asarray
     ci_h, va_h, B_h = to_h(prob.col_idx[:n]), to_h(prob.values[:n]), to_h(prob.B)
-    for i in range(ns.warmup + ns.steps):
+    C_h = np.zeros((rows, prob.Nd), np.float32)
+    for i in range(max(ns.warmup, 1) + ns.steps):
         t0 = time.perf_counter()
-        oracle.spmm(rp_h, ci_h, va_h, B_h, threads=threads)
-        if i >= ns.warmup:
+        oracle.spmm(rp_h, ci_h, va_h, B_h, threads=threads, out=C_h)
+        if i >= max(ns.warmup, 1):
             times.append(time.perf_counter() - t0)
     sec = float(np.mean(times))
     gflops = 2.0 * n * prob.Nd / sec / 1e9
@@ -489,6 +494,7 @@ def main(argv=None):
                      "traffic": ncu_traffic(prob.name, chosen, my_nnz), "peak_kind": f"of {peak_kind}",
                      "algorithmic_bytes": my_bytes, "b_rows_touched": touched,
                      "gather_bytes": gather_bytes, "gather_GBps": gather_bytes / sec / 1e9,
+                     "gather_frac": gather_bytes / sec / 1e9 / peak,
                      "scope": "rank 0's row block, main kernel + fix-up kernel"},
         "clocks": clocks.summary(),
     }
@@ -503,7 +509,7 @@ def main(argv=None):
         g, n_s, best = cpu_sample(torch, G, oracle, prob, rows, oracle.max_threads())
         line["cpu_baseline"] = {"value": g, "unit": "GFLOPS", "cores": oracle.max_threads(), "kind": "port",
                                 "sample": f"rows [0, {rows}) of {M} ({n_s} of {nnz} nnz), B complete on the host, "
-                                          f"best of 2, {best:.2f} s"}
+                                          f"best of 3 passes, {best:.2f} s per pass"}
         line["cusparse"] = cusparse_summary(
             cusparse_direct(torch, t, my_rows, Kd, Nd, my_nnz, C_out, min(ns.steps, 5), 2, flush_buf), flops_total)
         del prob, t, B, C_out, workspace, shard

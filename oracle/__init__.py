@@ -99,7 +99,7 @@ def max_threads() -> int:
 
 
 def spmm(row_ptr, col_idx, values, B, C_in=None, alpha=1.0, beta=0.0, *, fused=True, ncols=None,
-         threads=1) -> np.ndarray:
+         threads=1, out=None) -> np.ndarray:
     """alpha*A*B + beta*C_in in fp32, each output accumulated sequentially in stored order.
 
     ``fused=True`` accumulates with fmaf (what the GPU kernels do); ``fused=False`` rounds the
@@ -109,7 +109,13 @@ def spmm(row_ptr, col_idx, values, B, C_in=None, alpha=1.0, beta=0.0, *, fused=T
     """
     row_ptr, col_idx, values, B = _i32(row_ptr), _i32(col_idx), _f32(values), _f32(B)
     M, Nd = row_ptr.shape[0] - 1, B.shape[1]
-    out = np.zeros((M, Nd), np.float32) if C_in is None else _f32(C_in).copy()
+    if out is not None:  # timing runs: write into a caller buffer that is already paged in
+        if out.dtype != np.float32 or out.shape != (M, Nd) or not out.flags.c_contiguous:
+            raise ValueError("out must be a C-contiguous float32 array of shape (M, Nd)")
+        if C_in is not None:
+            out[...] = C_in
+    else:
+        out = np.zeros((M, Nd), np.float32) if C_in is None else _f32(C_in).copy()
     if beta != 0.0 and C_in is None:
         raise ValueError("beta != 0 needs C_in")
     lib().oracle_spmm_f32(M, Nd, Nd if ncols is None else int(ncols), _p(row_ptr, _i32p),
