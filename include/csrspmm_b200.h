@@ -52,8 +52,8 @@ typedef enum csrspmm_b200_status {
 } csrspmm_b200_status;
 
 /* Which of the reference's entry points the caller is serving (same order as
- * csrspmm::Algorithm, include/csrspmm/csrspmm.h:10-17).  It is a hint for kernel selection;
- * every value computes the same C. */
+ * csrspmm::Algorithm, include/csrspmm/csrspmm.h:10-17).  Recorded for diagnostics; every value
+ * computes the same C with the same automatically chosen kernel. */
 typedef enum csrspmm_b200_entry {
     CSRSPMM_B200_ENTRY_NAIVE = 0,
     CSRSPMM_B200_ENTRY_NAIVE_SMEM = 1,

@@ -506,3 +506,20 @@ except _lib.SpmmError as e:
     env = dict(__import__("os").environ, CSRSPMM_VALIDATE="1")
     out = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, env=env, timeout=300)
     assert out.returncode == 0 and "refused" in out.stdout, out.stdout + out.stderr
+
+
+def test_host_round_trip_with_packed_values(cuda_lib):
+    """csrspmm_b200_spmm_host with e2m1 values (host buffers, C large enough for the row-block path)."""
+    import ctypes as C
+    p = G.make("cfg3_powerlaw", scale=8, Nd=128)
+    packed, scale = ops.e2m1_quantize(p.values)
+    decoded = oracle.e2m1_decode(packed.numpy(), p.nnz, scale)
+    pk = packed.pin_memory()
+    h = [torch.from_numpy(x).pin_memory() for x in (p.row_ptr, p.col_idx, p.B)]
+    C_host = torch.empty(p.M, p.Nd).pin_memory()
+    a = _lib.make_args(p.M, p.Kd, p.Nd, p.nnz, h[0].data_ptr(), h[1].data_ptr(), pk.data_ptr(), h[2].data_ptr(),
+                       C_host.data_ptr(), value_format=_lib.VALUES_E2M1, value_scale=scale)
+    st = cuda_lib.csrspmm_b200_spmm_host(C.byref(a), None, 0, C.c_void_p(torch.cuda.current_stream().cuda_stream))
+    assert st == _lib.OK, cuda_lib.csrspmm_b200_last_error()
+    f64, mag = oracle.spmm_f64(p.row_ptr, p.col_idx, decoded, p.B, threads=4)
+    assert (np.abs(C_host.numpy() - f64) <= 1e-4 * mag + 1e-6).all()
