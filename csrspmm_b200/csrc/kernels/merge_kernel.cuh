@@ -344,16 +344,37 @@ __global__ void __launch_bounds__(256) spmm_fixup_kernel(const SpmmParams p, int
     const int row = __ldg(p.carry_row + t);
     if (row < 0 || row >= p.M) return;
     if (t > 0 && __ldg(p.carry_row + t - 1) == row) return;
+    // end of the run of tiles that carry this row: 32 tiles examined per step, so that a row
+    // spread over thousands of tiles (a hub row) is not a chain of dependent loads
     int e = t + 1;
-    while (e < num_tiles && __ldg(p.carry_row + e) == row) ++e;
+    for (;;) {
+        const int idx = e + lane;
+        const bool same = idx < num_tiles && __ldg(p.carry_row + idx) == row;
+        const unsigned m = __ballot_sync(0xffffffffu, same);
+        if (m == 0xffffffffu) {
+            e += 32;
+            continue;
+        }
+        e += __ffs(~m) - 1;
+        break;
+    }
 
     float* crow = p.C + (long long)row * p.ldc;
     for (int cv = lane; cv < p.ncolv; cv += 32) {
+        const float* src = p.carry_val + (long long)cv * VW;
         Vec<VW> sum;
-        sum.load(p.carry_val + (long long)t * p.carry_ld + (long long)cv * VW);
-        for (int q = t + 1; q < e; ++q) {
+        sum.load(src + (long long)t * p.carry_ld);
+        int q = t + 1;
+        for (; q + 8 <= e; q += 8) {  // eight loads in flight, added in tile order
+            Vec<VW> x[8];
+#pragma unroll
+            for (int k = 0; k < 8; ++k) x[k].load(src + (long long)(q + k) * p.carry_ld);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) sum.add(x[k]);
+        }
+        for (; q < e; ++q) {
             Vec<VW> x;
-            x.load(p.carry_val + (long long)q * p.carry_ld + (long long)cv * VW);
+            x.load(src + (long long)q * p.carry_ld);
             sum.add(x);
         }
         Vec<VW> old;

@@ -523,3 +523,29 @@ def test_host_round_trip_with_packed_values(cuda_lib):
     assert st == _lib.OK, cuda_lib.csrspmm_b200_last_error()
     f64, mag = oracle.spmm_f64(p.row_ptr, p.col_idx, decoded, p.B, threads=4)
     assert (np.abs(C_host.numpy() - f64) <= 1e-4 * mag + 1e-6).all()
+
+
+@pytest.mark.parametrize("kernel", ["merge", "tma"])
+def test_hub_row_spread_over_thousands_of_tiles(cuda_lib, kernel):
+    """One row holding 3 million non-zeros (a hub of a graph) among ordinary rows: its partial sums come
+    from about 3000 tiles and are added up by the fix-up kernel in tile order."""
+    import types
+    Kd = 65536
+    rng = np.random.default_rng(71)
+    lens = np.full(2000, 5, np.int64)
+    lens[700] = 3_000_000
+    lens[1500] = 40_000
+    row_ptr = np.zeros(len(lens) + 1, np.int32)
+    np.cumsum(lens, out=row_ptr[1:])
+    nnz = int(row_ptr[-1])
+    # columns unsorted and repeated: the kernels take stored order as it comes
+    p = types.SimpleNamespace(row_ptr=row_ptr, col_idx=rng.integers(0, Kd, nnz).astype(np.int32),
+                              values=rng.uniform(0.0, 1.0, nnz).astype(np.float32))
+    ones = np.ones((Kd, 64), np.float32)  # C[r, :] = sum of the row's values: checkable without a dense oracle pass
+    rp, ci, va = dev(p.row_ptr), dev(p.col_idx), dev(p.values)
+    got = ops.spmm(rp, ci, va, dev(ones), kernel=kernel, sync=True).cpu().numpy()
+    want = np.add.reduceat(p.values.astype(np.float64), p.row_ptr[:-1].astype(np.int64))
+    assert np.allclose(got[:, 0], want, rtol=1e-5, atol=1e-4)
+    assert (got == got[:, :1]).all()
+    again = ops.spmm(rp, ci, va, dev(ones), kernel=kernel, sync=True).cpu().numpy()
+    assert np.array_equal(got, again)  # fixed summation order
