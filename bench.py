@@ -316,6 +316,8 @@ def main(argv=None):
     ap.add_argument("--kernel", default="auto", choices=["auto", "row", "merge", "tma"])
     ap.add_argument("--no-extras", action="store_true", help="skip e2e, cpu_baseline and other_workloads")
     ap.add_argument("--e2e-steps", type=int, default=3)
+    ap.add_argument("--e2e-panels", type=int, default=0,
+                    help="column panels of the host round trip (0 = the library's rule, 1 = no panels)")
     ns = ap.parse_args(argv)
     ns.warmup = max(ns.warmup, 3) if ns.impl == "ours" else ns.warmup
 
@@ -431,13 +433,18 @@ def main(argv=None):
             C_host = torch.empty((my_rows, Nd), dtype=torch.float32, pin_memory=True)
             arena = torch.empty(ops.host_arena_bytes(my_rows, Kd, Nd, my_nnz), dtype=torch.uint8, device=dev)
 
+            if ns.e2e_panels > 0:
+                os.environ["CSRSPMM_HOST_PANELS"] = str(ns.e2e_panels)
+            n_panels = len(D.column_panels(Kd, Nd, ns.e2e_panels or None))
+
             def e2e_step():
                 ops.spmm_host(h["row_ptr"], h["col_idx"], h["values"], h["B"], C_host, 1.0, 0.0, kernel=ns.kernel,
                               arena=arena, device=dev)
 
             h2d = my_nnz * 8 + (my_rows + 1) * 4 + Kd * Nd * 4
             d2h, xchg = my_rows * Nd * 4, 0
-            api = "csrspmm_b200_spmm_host (pinned host A, B in; host C out in row blocks overlapped with compute)"
+            api = (f"csrspmm_b200_spmm_host (pinned host A, B in, host C out; {n_panels} column panel(s): uploads, "
+                   "kernels and downloads of different panels overlap)")
         else:
             sl = Kd // world
             hs = D.Shard(rank, world, shard.row_lo, shard.row_hi,
@@ -446,11 +453,12 @@ def main(argv=None):
             hB = B[rank * sl:(rank + 1) * sl].cpu().pin_memory()
             del t, B, shard, C_out, workspace
             torch.cuda.empty_cache()
-            runner = D.ShardedHostSpmm(hs, hB, Kd, dev, kernel=ns.kernel)
+            runner = D.ShardedHostSpmm(hs, hB, Kd, dev, kernel=ns.kernel, panels=ns.e2e_panels or None)
             e2e_step = runner.run
+            n_panels = len(runner.panels)
             h2d, d2h, xchg = runner.h2d_bytes, runner.d2h_bytes, runner.exchange_bytes
             api = ("distributed.ShardedHostSpmm (per rank: pinned host block of A and 1/N of B in, NCCL all-gather of "
-                   "B, host block of C out)")
+                   f"B, host block of C out; {n_panels} column panel(s) pipelined over three streams)")
         torch.cuda.synchronize()
         e2e_step()  # warm-up
         barrier()
@@ -466,7 +474,7 @@ def main(argv=None):
         same = D.sum_over_ranks(0.0 if same else 1.0, dev) == 0.0
         e2e = {"value": flops_total / e2e_sec / 1e9, "matches_device_run": same, "unit": "GFLOPS", "h2d_bytes_per_step": int(h2d),
                "d2h_bytes_per_step": int(d2h), "nvlink_bytes_per_step": int(xchg), "ms_per_step": e2e_sec * 1e3,
-               "steps": ns.e2e_steps, "bytes_are": "per rank", "api": api}
+               "steps": ns.e2e_steps, "bytes_are": "per rank", "column_panels": n_panels, "api": api}
 
     if world > 1:
         barrier()

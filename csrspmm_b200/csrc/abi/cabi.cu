@@ -222,6 +222,120 @@ int enqueue(const csrspmm_b200_args* a, cudaStream_t st)
 
 size_t align256(size_t v) { return (v + 255) / 256 * 256; }
 
+// ---- host round trip in column panels -------------------------------------------------------
+//
+// C[:, panel] depends on B[:, panel] only, so a wide product whose operands start in host memory
+// can be cut into column panels: while panel q is being multiplied, panel q+1 of B is still
+// arriving and panel q-1 of C is already leaving, which keeps both directions of the host link
+// busy at once.  Each output element is still one sequential sum, so the result equals the
+// unsplit product bit for bit.  On the device a panel is stored contiguously (ld = its width).
+constexpr int kMaxPanels = 16;
+
+// Number of column panels for a host round trip: the environment variable
+// CSRSPMM_HOST_PANELS (1 = off) or, for a B of 256 MiB and more, panels of 128 columns
+// (512-byte segments in the strided host copies), at most eight.
+int host_panel_count(const csrspmm_b200_args* a)
+{
+    int want = 0;
+    if (const char* e = std::getenv("CSRSPMM_HOST_PANELS")) want = std::atoi(e);
+    if (want <= 0) {
+        const size_t b_bytes = (size_t)a->Kd * (size_t)a->Nd * 4;
+        want = (b_bytes >= ((size_t)256 << 20) && a->Nd >= 256) ? a->Nd / 128 : 1;
+        if (want > 8) want = 8;
+    }
+    if (want > kMaxPanels) want = kMaxPanels;
+    if (want > a->Nd / 32) want = a->Nd / 32;  // never narrower than 32 columns
+    return want < 1 ? 1 : want;
+}
+
+struct HostBuffers {
+    int32_t* rp;
+    int32_t* ci;
+    char* va;
+    float* B;
+    float* C;
+    void* ws;
+    size_t ws_bytes;
+    int32_t* status;
+};
+
+int spmm_host_panels(const csrspmm_b200_args* a, const HostBuffers& d, int panels, cudaStream_t st, int* word)
+{
+    // panel width: a multiple of 32 columns, so every panel but the last keeps the vector layout
+    int pw = ((a->Nd + panels - 1) / panels + 31) / 32 * 32;
+    panels = (a->Nd + pw - 1) / pw;
+
+    cudaStream_t compute = nullptr, out = nullptr;
+    cudaEvent_t up[kMaxPanels] = {}, done[kMaxPanels] = {};
+    int n_up = 0, n_done = 0;
+    auto cleanup = [&]() {
+        for (int k = 0; k < n_up; ++k) cudaEventDestroy(up[k]);
+        for (int k = 0; k < n_done; ++k) cudaEventDestroy(done[k]);
+        if (compute) cudaStreamDestroy(compute);
+        if (out) cudaStreamDestroy(out);
+    };
+#define CUDA_TRY_PANEL(expr)                                                                \
+    do {                                                                                    \
+        cudaError_t e__ = (expr);                                                           \
+        if (e__ != cudaSuccess) {                                                           \
+            set_last_error("%s failed: %s", #expr, cudaGetErrorString(e__));                \
+            cudaDeviceSynchronize();                                                        \
+            cleanup();                                                                      \
+            return CSRSPMM_B200_ERR_CUDA;                                                   \
+        }                                                                                   \
+    } while (0)
+
+    CUDA_TRY_PANEL(cudaStreamCreateWithFlags(&compute, cudaStreamNonBlocking));
+    CUDA_TRY_PANEL(cudaStreamCreateWithFlags(&out, cudaStreamNonBlocking));
+    for (; n_up < panels; ++n_up) CUDA_TRY_PANEL(cudaEventCreateWithFlags(&up[n_up], cudaEventDisableTiming));
+    for (; n_done < panels; ++n_done) CUDA_TRY_PANEL(cudaEventCreateWithFlags(&done[n_done], cudaEventDisableTiming));
+
+    for (int q = 0; q < panels; ++q) {
+        const int c0 = q * pw;
+        const int w = (a->Nd - c0 < pw) ? a->Nd - c0 : pw;
+        float* dB = d.B + (size_t)a->Kd * (size_t)c0;
+        float* dC = d.C + (size_t)a->M * (size_t)c0;
+        if (a->beta != 0.0f)
+            CUDA_TRY_PANEL(cudaMemcpy2DAsync(dC, (size_t)w * 4, a->C + c0, (size_t)a->ldc * 4, (size_t)w * 4,
+                                             (size_t)a->M, cudaMemcpyHostToDevice, st));
+        if (a->Kd > 0)
+            CUDA_TRY_PANEL(cudaMemcpy2DAsync(dB, (size_t)w * 4, a->B + c0, (size_t)a->ldb * 4, (size_t)w * 4,
+                                             (size_t)a->Kd, cudaMemcpyHostToDevice, st));
+        CUDA_TRY_PANEL(cudaEventRecord(up[q], st));
+        CUDA_TRY_PANEL(cudaStreamWaitEvent(compute, up[q], 0));
+
+        csrspmm_b200_args pa = *a;
+        pa.Nd = w;
+        pa.row_ptr = d.rp;
+        pa.col_idx = d.ci;
+        pa.values = d.va;
+        pa.B = dB;
+        pa.ldb = w;
+        pa.C = dC;
+        pa.ldc = w;
+        pa.workspace = d.ws;
+        pa.workspace_bytes = d.ws_bytes;
+        pa.status_word = d.status;
+        const int status = enqueue(&pa, compute);
+        if (status != CSRSPMM_B200_OK) {
+            cudaDeviceSynchronize();
+            cleanup();
+            return status;
+        }
+        CUDA_TRY_PANEL(cudaEventRecord(done[q], compute));
+        CUDA_TRY_PANEL(cudaStreamWaitEvent(out, done[q], 0));
+        CUDA_TRY_PANEL(cudaMemcpy2DAsync(a->C + c0, (size_t)a->ldc * 4, dC, (size_t)w * 4, (size_t)w * 4, (size_t)a->M,
+                                         cudaMemcpyDeviceToHost, out));
+    }
+    CUDA_TRY_PANEL(cudaMemcpyAsync(word, d.status, 4, cudaMemcpyDeviceToHost, compute));
+    CUDA_TRY_PANEL(cudaStreamSynchronize(compute));
+    CUDA_TRY_PANEL(cudaStreamSynchronize(out));
+    CUDA_TRY_PANEL(cudaStreamSynchronize(st));
+    cleanup();
+    return CSRSPMM_B200_OK;
+#undef CUDA_TRY_PANEL
+}
+
 }  // namespace
 
 extern "C" {
@@ -334,6 +448,37 @@ int csrspmm_b200_spmm_host(const csrspmm_b200_args* a, void* device_arena, size_
     void* d_ws = cur; cur += align256(ws_bytes);
     int32_t* d_status = reinterpret_cast<int32_t*>(cur);
 
+    const int panels = host_panel_count(a);
+    if (panels > 1) {
+        // A first, on the caller's stream; the panels of B follow it on the same stream
+        int word = 0;
+        cudaError_t e = cudaMemsetAsync(d_status, 0, 4, st);
+        if (e == cudaSuccess) e = cudaMemcpyAsync(d_rp, a->row_ptr, rp_bytes, cudaMemcpyHostToDevice, st);
+        if (e == cudaSuccess && a->nnz > 0) e = cudaMemcpyAsync(d_ci, a->col_idx, ci_bytes, cudaMemcpyHostToDevice, st);
+        if (e == cudaSuccess && a->nnz > 0) e = cudaMemcpyAsync(d_va, a->values, vbytes, cudaMemcpyHostToDevice, st);
+        if (e != cudaSuccess) {
+            set_last_error("spmm_host: upload of A failed: %s", cudaGetErrorString(e));
+            status = CSRSPMM_B200_ERR_CUDA;
+        } else {
+            const HostBuffers hb = {d_rp, d_ci, d_va, d_B, d_C, d_ws, align256(ws_bytes), d_status};
+            status = spmm_host_panels(a, hb, panels, st, &word);
+        }
+        if (owned) {
+            cudaFreeAsync(arena, st);
+            cudaStreamSynchronize(st);
+        }
+        if (status != CSRSPMM_B200_OK) return status;
+        if (word & kStatusWaitTimeout) {
+            set_last_error("device status word 0x%x: a bounded wait gave up", word);
+            return CSRSPMM_B200_ERR_DEVICE_WAIT;
+        }
+        if (word != 0) {
+            set_last_error("device status word 0x%x: malformed CSR (row_ptr or col_idx)", word);
+            return CSRSPMM_B200_ERR_INVALID_CSR;
+        }
+        return CSRSPMM_B200_OK;
+    }
+
     // C goes back in row blocks on a second stream while the next block is being computed, so
     // the device->host copy of a large C hides the kernel time (and vice versa).
     constexpr int kMaxBlocks = 8;
@@ -431,6 +576,20 @@ int csrspmm_b200_spmm_host(const csrspmm_b200_args* a, void* device_arena, size_
     }
     return CSRSPMM_B200_OK;
 #undef CUDA_TRY_HOST
+}
+
+int csrspmm_b200_copy_rows(void* dst, size_t dst_pitch_bytes, const void* src, size_t src_pitch_bytes,
+                           size_t width_bytes, size_t rows, int to_host, csrspmm_b200_stream_t stream)
+{
+    if (width_bytes == 0 || rows == 0) return CSRSPMM_B200_OK;
+    if (dst == nullptr || src == nullptr || dst_pitch_bytes < width_bytes || src_pitch_bytes < width_bytes) {
+        set_last_error("copy_rows: null pointer or pitch smaller than the row width");
+        return CSRSPMM_B200_ERR_BAD_ARG;
+    }
+    CUDA_TRY(cudaMemcpy2DAsync(dst, dst_pitch_bytes, src, src_pitch_bytes, width_bytes, rows,
+                               to_host ? cudaMemcpyDeviceToHost : cudaMemcpyHostToDevice,
+                               reinterpret_cast<cudaStream_t>(stream)));
+    return CSRSPMM_B200_OK;
 }
 
 int csrspmm_b200_validate_csr_device(int32_t M, int32_t Kd, int64_t nnz, const int32_t* row_ptr,

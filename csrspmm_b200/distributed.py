@@ -101,6 +101,17 @@ def sum_over_ranks(value: float, device) -> float:
     return float(t.item())
 
 
+def column_panels(Kd: int, Nd: int, panels: int | None = None):
+    """[(first column, width)] of the column panels a host round trip is cut into.  ``panels`` None
+    applies the library's rule (a B of 256 MiB or more with Nd >= 256: panels of 128 columns, at
+    most eight); widths are multiples of 32 columns except possibly the last."""
+    if panels is None:
+        panels = min(Nd // 128, 8) if (Kd * Nd * 4 >= (256 << 20) and Nd >= 256) else 1
+    panels = max(1, min(int(panels), 16, max(Nd // 32, 1)))
+    pw = ((Nd + panels - 1) // panels + 31) // 32 * 32 if panels > 1 else Nd
+    return [(c0, min(pw, Nd - c0)) for c0 in range(0, max(Nd, 1), max(pw, 1))] if Nd > 0 else [(0, 0)]
+
+
 class ShardedHostSpmm:
     """End-to-end product from HOST memory on several GPUs: every rank uploads only its own part.
 
@@ -109,9 +120,16 @@ class ShardedHostSpmm:
     NVLink into the full device copy of B (the one exchange this path has: each byte of B
     crosses PCIe once instead of once per GPU), multiply, download the block of C.  With a
     single rank there is no exchange and this is the plain host round trip.
+
+    A wide product runs in column panels (``column_panels``): C[:, panel] needs B[:, panel] only,
+    so while panel q is gathered and multiplied, panel q+1 of the B slice is still arriving over
+    PCIe and panel q-1 of C is already leaving -- uploads, NVLink exchange, kernels and downloads of
+    different panels run at the same time on three streams.  On the device each panel of B and
+    of C is stored contiguously; every element of C is the same sum as in the unsplit product.
     """
 
-    def __init__(self, shard_host: "Shard", B_slice_host: torch.Tensor, Kd: int, device, kernel: str = "auto"):
+    def __init__(self, shard_host: "Shard", B_slice_host: torch.Tensor, Kd: int, device, kernel: str = "auto",
+                 panels: int | None = None):
         import torch.distributed as dist
         from . import ops
         self.dist, self.ops, self.dev = dist, ops, torch.device(device)
@@ -125,27 +143,50 @@ class ShardedHostSpmm:
         self.d_rp = torch.empty(rows + 1, dtype=torch.int32, device=d)
         self.d_ci = torch.empty(shard_host.nnz, dtype=torch.int32, device=d)
         self.d_va = torch.empty(shard_host.nnz, dtype=torch.float32, device=d)
-        self.d_B = torch.empty((Kd, Nd), dtype=torch.float32, device=d)
-        self.d_C = torch.empty((rows, Nd), dtype=torch.float32, device=d)
         self.C_host = torch.empty((rows, Nd), dtype=torch.float32, pin_memory=True)
         self.slice_rows = Kd // self.world
-        self.call = ops.SpmmCall(self.d_rp, self.d_ci, self.d_va, self.d_B, self.d_C, 1.0, 0.0, kernel=kernel)
+        self.panels = column_panels(Kd, Nd, panels)
+        flat_B = torch.empty(Kd * Nd, dtype=torch.float32, device=d)
+        flat_C = torch.empty(rows * Nd, dtype=torch.float32, device=d)
+        self.d_B = [flat_B[Kd * c0:Kd * (c0 + w)].view(Kd, w) for c0, w in self.panels]
+        self.d_C = [flat_C[rows * c0:rows * (c0 + w)].view(rows, w) for c0, w in self.panels]
+        self.calls, ws = [], None
+        for Bq, Cq in zip(self.d_B, self.d_C):  # widest panel first, so its scratch serves the others
+            call = ops.SpmmCall(self.d_rp, self.d_ci, self.d_va, Bq, Cq, 1.0, 0.0, kernel=kernel,
+                                max_row_nnz=shard_host.max_row_nnz, workspace=ws)
+            ws = call._keep[5] if ws is None else ws
+            self.calls.append(call)
+        with torch.cuda.device(d):
+            self.s_up, self.s_mul, self.s_down = torch.cuda.Stream(d), torch.cuda.Stream(d), torch.cuda.Stream(d)
+            self.ev_up = [torch.cuda.Event() for _ in self.panels]
+            self.ev_mul = [torch.cuda.Event() for _ in self.panels]
         self.h2d_bytes = (rows + 1) * 4 + shard_host.nnz * 8 + self.slice_rows * Nd * 4
         self.d2h_bytes = rows * Nd * 4
         self.exchange_bytes = (Kd - self.slice_rows) * Nd * 4  # received over NVLink per rank
 
     def run(self) -> torch.Tensor:
-        k0 = self.rank * self.slice_rows
-        mine = self.d_B[k0:k0 + self.slice_rows]
-        self.d_rp.copy_(self.h_rp, non_blocking=True)
-        self.d_ci.copy_(self.h_ci, non_blocking=True)
-        self.d_va.copy_(self.h_va, non_blocking=True)
-        mine.copy_(self.h_B, non_blocking=True)
-        if self.world > 1:
-            self.dist.all_gather_into_tensor(self.d_B, mine)  # in place: slice g already sits at offset g
-        self.call()
-        self.C_host.copy_(self.d_C, non_blocking=True)
-        torch.cuda.current_stream(self.dev).synchronize()
+        k0, k1 = self.rank * self.slice_rows, (self.rank + 1) * self.slice_rows
+        self.s_up.wait_stream(torch.cuda.current_stream(self.dev))
+        with torch.cuda.stream(self.s_up):
+            self.d_rp.copy_(self.h_rp, non_blocking=True)
+            self.d_ci.copy_(self.h_ci, non_blocking=True)
+            self.d_va.copy_(self.h_va, non_blocking=True)
+        for q, (c0, w) in enumerate(self.panels):
+            mine = self.d_B[q][k0:k1]
+            with torch.cuda.stream(self.s_up):
+                self.ops.copy_rows(mine, self.h_B[:, c0:c0 + w])
+                self.ev_up[q].record()
+            with torch.cuda.stream(self.s_mul):
+                self.s_mul.wait_event(self.ev_up[q])
+                if self.world > 1:
+                    self.dist.all_gather_into_tensor(self.d_B[q], mine)  # in place: slice g already sits at offset g
+                self.calls[q]()
+                self.ev_mul[q].record()
+            with torch.cuda.stream(self.s_down):
+                self.s_down.wait_event(self.ev_mul[q])
+                self.ops.copy_rows(self.C_host[:, c0:c0 + w], self.d_C[q])
+        self.s_mul.synchronize()
+        self.s_down.synchronize()
         return self.C_host
 
 

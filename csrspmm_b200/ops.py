@@ -299,6 +299,28 @@ def spmm_host(row_ptr, col_idx, values, B, C_host, alpha=1.0, beta=0.0, *, entry
     return C_host
 
 
+def copy_rows(dst: torch.Tensor, src: torch.Tensor) -> None:
+    """Asynchronous strided copy between a host matrix and a CUDA matrix of the same shape, on the
+    current stream of the CUDA side.  Either side may be a column slice of a wider row-major matrix
+    (rows keep their pitch), which ``Tensor.copy_`` would first repack on the host."""
+    if dst.shape != src.shape or dst.dim() != 2 or dst.dtype != src.dtype or dst.is_cuda == src.is_cuda:
+        raise RuntimeError("copy_rows wants two 2-D tensors of one shape and dtype, one on the host and one on a GPU")
+    rows, cols = dst.shape
+    if rows == 0 or cols == 0:
+        return
+    if (cols > 1 and (dst.stride(1) != 1 or src.stride(1) != 1)):
+        raise RuntimeError("copy_rows wants unit stride along the rows")
+    es = dst.element_size()
+    dpitch = (dst.stride(0) if rows > 1 else cols) * es
+    spitch = (src.stride(0) if rows > 1 else cols) * es
+    dev = dst.device if dst.is_cuda else src.device
+    with torch.cuda.device(dev):
+        st = _lib.lib().csrspmm_b200_copy_rows(dst.data_ptr(), dpitch, src.data_ptr(), spitch, cols * es, rows,
+                                               0 if dst.is_cuda else 1,
+                                               C.c_void_p(torch.cuda.current_stream(dev).cuda_stream))
+    _lib.check(st, "csrspmm_b200_copy_rows")
+
+
 def host_arena_bytes(M, Kd, Nd, nnz) -> int:
     a = _lib.make_args(M, Kd, Nd, nnz)
     return int(_lib.lib().csrspmm_b200_host_arena_bytes(C.byref(a)))

@@ -124,10 +124,23 @@ int csrspmm_b200_spmm_sync(const csrspmm_b200_args* args, csrspmm_b200_stream_t 
 /* Host pointers in `args` (workspace/status_word ignored).  Copies A and B (and C when
  * beta != 0) to the current device, runs the SpMM, copies C back and waits.  When
  * device_arena is NULL the device buffers are allocated and released inside the call; else
- * the arena (>= csrspmm_b200_host_arena_bytes(args) bytes, 256-byte aligned) is used. */
+ * the arena (>= csrspmm_b200_host_arena_bytes(args) bytes, 256-byte aligned) is used.
+ * Copies and kernels overlap: a B of 256 MiB or more with Nd >= 256 is processed in column panels
+ * of 128 columns (panel q+1 of B arrives and panel q-1 of C leaves while panel q is multiplied;
+ * CSRSPMM_HOST_PANELS=<n> in the environment sets the number of panels, 1 = none); otherwise a
+ * large C goes back in row blocks while the next block is computed.  Either way every element of
+ * C is the same sequential sum as in one unsplit product. */
 int csrspmm_b200_spmm_host(const csrspmm_b200_args* args, void* device_arena,
                            size_t device_arena_bytes, csrspmm_b200_stream_t stream);
 size_t csrspmm_b200_host_arena_bytes(const csrspmm_b200_args* args);
+
+/* No counterpart in the reference (its dense_host2device / dense_device2host,
+ * src/host/dense_utils.cpp, copy whole packed matrices).  Asynchronous copy of `rows` rows of
+ * `width_bytes` bytes between host and device, each side with its own pitch -- what a caller
+ * needs to move one column panel of a row-major matrix.  to_host = 0: src is host memory, dst
+ * device memory; to_host = 1: the other way.  Pinned host memory makes it truly asynchronous. */
+int csrspmm_b200_copy_rows(void* dst, size_t dst_pitch_bytes, const void* src, size_t src_pitch_bytes,
+                           size_t width_bytes, size_t rows, int to_host, csrspmm_b200_stream_t stream);
 
 /* No counterpart in the reference.  The same product as csrspmm_b200_spmm for callers that cannot
  * obtain device memory at call time -- a process whose memory manager already owns the whole GPU,

@@ -549,3 +549,76 @@ def test_hub_row_spread_over_thousands_of_tiles(cuda_lib, kernel):
     assert (got == got[:, :1]).all()
     again = ops.spmm(rp, ci, va, dev(ones), kernel=kernel, sync=True).cpu().numpy()
     assert np.array_equal(got, again)  # fixed summation order
+
+
+@pytest.mark.parametrize("panels,Nd", [(3, 200), (4, 512), (2, 70)])
+def test_host_round_trip_in_column_panels(cuda_lib, monkeypatch, panels, Nd):
+    """csrspmm_b200_spmm_host cut into column panels (CSRSPMM_HOST_PANELS): strided host operands, ragged
+    last panel, beta != 0; even rows and the longest row given, so the whole-row kernel runs in every
+    panel and the result matches the oracle bit for bit."""
+    p = G.random_csr(3000, 2500, Nd, 0.004, seed=91)
+    want = oracle.spmm(*arrays(p), threads=4)
+    mx = int(np.diff(p.row_ptr).max())
+    hB = torch.zeros(p.Kd, Nd + 24).pin_memory()  # ldb > Nd
+    hB[:, :Nd] = torch.from_numpy(p.B)
+    hC = torch.full((p.M, Nd + 8), 7.0).pin_memory()  # ldc > Nd; the padding must stay untouched
+    h = [torch.from_numpy(x).pin_memory() for x in (p.row_ptr, p.col_idx, p.values)]
+    monkeypatch.setenv("CSRSPMM_HOST_PANELS", str(panels))
+    ops.spmm_host(*h, hB[:, :Nd], hC[:, :Nd], max_row_nnz=mx)
+    assert np.array_equal(hC[:, :Nd].numpy(), want)
+    assert (hC[:, Nd:] == 7.0).all()
+    monkeypatch.setenv("CSRSPMM_HOST_PANELS", "1")
+    one = torch.empty(p.M, Nd).pin_memory()
+    ops.spmm_host(*h, hB[:, :Nd], one, max_row_nnz=mx)
+    assert np.array_equal(one.numpy(), want)
+    # beta != 0: each panel of C goes up before it is multiplied
+    monkeypatch.setenv("CSRSPMM_HOST_PANELS", str(panels))
+    C0 = np.random.default_rng(5).standard_normal((p.M, Nd)).astype(np.float32)
+    hC[:, :Nd] = torch.from_numpy(C0)
+    ops.spmm_host(*h, hB[:, :Nd], hC[:, :Nd], 1.5, -0.25, max_row_nnz=mx)
+    want_b = oracle.spmm(*arrays(p), C0.copy(), 1.5, -0.25, threads=4)
+    assert np.allclose(hC[:, :Nd].numpy(), want_b, rtol=RTOL, atol=ATOL)
+    assert (hC[:, Nd:] == 7.0).all()
+
+
+def test_host_round_trip_in_column_panels_split_rows(cuda_lib, monkeypatch):
+    """Column panels on a skewed matrix (merge-path kernel inside each panel)."""
+    p = G.make("cfg3_powerlaw", scale=32, Nd=256)
+    h = [torch.from_numpy(x).pin_memory() for x in arrays(p)]
+    C_host = torch.empty(p.M, p.Nd).pin_memory()
+    monkeypatch.setenv("CSRSPMM_HOST_PANELS", "4")
+    ops.spmm_host(*h, C_host)
+    f64, mag = oracle.spmm_f64(p.row_ptr, p.col_idx, p.values, p.B, threads=4)
+    assert (np.abs(C_host.numpy() - f64) <= RTOL * mag + ATOL).all()
+
+
+def test_copy_rows_moves_column_slices(cuda_lib):
+    host = torch.arange(50 * 40, dtype=torch.float32).view(50, 40).pin_memory()
+    d = torch.zeros(50, 16, device="cuda")
+    ops.copy_rows(d, host[:, 8:24])
+    torch.cuda.synchronize()
+    assert torch.equal(d.cpu(), host[:, 8:24])
+    back = torch.full((50, 40), -1.0).pin_memory()
+    ops.copy_rows(back[:, 3:19], d)
+    torch.cuda.synchronize()
+    assert torch.equal(back[:, 3:19], host[:, 8:24]) and (back[:, :3] == -1).all() and (back[:, 19:] == -1).all()
+    with pytest.raises(RuntimeError):
+        ops.copy_rows(d, d)
+
+
+@pytest.mark.parametrize("panels", [1, 3])
+def test_sharded_host_pipeline_single_rank(cuda_lib, panels):
+    """distributed.ShardedHostSpmm without a process group (one rank): the three-stream column-panel
+    pipeline gives the oracle's result, twice in a row."""
+    from csrspmm_b200 import distributed as D
+    p = G.random_csr(4000, 3000, 320, 0.003, seed=17)
+    want = oracle.spmm(*arrays(p), threads=4)
+    bounds = np.array([0, p.M], np.int32)
+    sh = D.take_shard(torch.from_numpy(p.row_ptr), torch.from_numpy(p.col_idx), torch.from_numpy(p.values), bounds, 0)
+    sh.row_ptr, sh.col_idx, sh.values = sh.row_ptr.pin_memory(), sh.col_idx.pin_memory(), sh.values.pin_memory()
+    runner = D.ShardedHostSpmm(sh, torch.from_numpy(p.B).pin_memory(), p.Kd, "cuda", panels=panels)
+    assert len(runner.panels) == panels
+    for _ in range(2):
+        runner.C_host.fill_(float("nan"))
+        got = runner.run()
+        assert np.array_equal(got.numpy(), want)
