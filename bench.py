@@ -315,6 +315,8 @@ def main(argv=None):
     ap.add_argument("--scale", type=int, default=1, help="divide M and Kd (for quick runs and ncu captures)")
     ap.add_argument("--kernel", default="auto", choices=["auto", "row", "merge", "tma"])
     ap.add_argument("--no-extras", action="store_true", help="skip e2e, cpu_baseline and other_workloads")
+    ap.add_argument("--only-e2e", action="store_true",
+                    help="keep e2e but skip the oracle check, cpu_baseline, cuSPARSE and other_workloads")
     ap.add_argument("--e2e-steps", type=int, default=3)
     ap.add_argument("--e2e-panels", type=int, default=0,
                     help="column panels of the host round trip (0 = the library's rule, 1 = no panels)")
@@ -403,7 +405,7 @@ def main(argv=None):
 
     # sanity: a sample of this rank's rows against the CPU oracle (outside every timed region)
     check = None
-    if rank == 0 and not ns.no_extras:
+    if rank == 0 and not ns.no_extras and not ns.only_e2e:
         import oracle
         rows = np.unique(np.concatenate([np.random.default_rng(0).integers(0, my_rows, 512),
                                          np.argsort(np.diff(shard.row_ptr.cpu().numpy()))[-4:]]))
@@ -511,7 +513,7 @@ def main(argv=None):
     if e2e is not None:
         line["e2e"] = e2e
 
-    if world == 1 and not ns.no_extras:
+    if world == 1 and not ns.no_extras and not ns.only_e2e:
         import oracle
         rows = sample_rows_for(ns.workload, M)
         g, n_s, best = cpu_sample(torch, G, oracle, prob, rows, oracle.max_threads())

@@ -35,7 +35,7 @@ EXPORTED_SYMBOLS = (
     "csrspmm_b200_validate_csr_host", "csrspmm_b200_validate_csr_device",
     "csrspmm_b200_row_stats_device", "csrspmm_b200_partition_rows", "csrspmm_b200_e2m1_scale",
     "csrspmm_b200_e2m1_encode", "csrspmm_b200_e2m1_decode", "csrspmm_b200_dense2csr_count",
-    "csrspmm_b200_dense2csr_fill", "csrspmm_b200_csr2dense", "csrspmm_b200_copy_rows",
+    "csrspmm_b200_dense2csr_fill", "csrspmm_b200_csr2dense", "csrspmm_b200_copy_rows", "csrspmm_b200_column_panels",
 )
 
 
@@ -103,6 +103,8 @@ def lib() -> C.CDLL:
         fn.restype = C.c_int
     L.csrspmm_b200_spmm_host.argtypes = [C.POINTER(Args), C.c_void_p, C.c_size_t, C.c_void_p]
     L.csrspmm_b200_spmm_host.restype = C.c_int
+    L.csrspmm_b200_column_panels.argtypes = [C.c_int32, C.c_int32, C.c_int, C.c_void_p, C.c_void_p]
+    L.csrspmm_b200_column_panels.restype = C.c_int
     L.csrspmm_b200_copy_rows.argtypes = [C.c_void_p, C.c_size_t, C.c_void_p, C.c_size_t, C.c_size_t, C.c_size_t,
                                          C.c_int, C.c_void_p]
     L.csrspmm_b200_copy_rows.restype = C.c_int

@@ -229,23 +229,34 @@ size_t align256(size_t v) { return (v + 255) / 256 * 256; }
 // arriving and panel q-1 of C is already leaving, which keeps both directions of the host link
 // busy at once.  Each output element is still one sequential sum, so the result equals the
 // unsplit product bit for bit.  On the device a panel is stored contiguously (ld = its width).
-constexpr int kMaxPanels = 16;
+constexpr int kMaxPanels = CSRSPMM_B200_MAX_PANELS;
 
-// Number of column panels for a host round trip: the environment variable
-// CSRSPMM_HOST_PANELS (1 = off) or, for a B of 256 MiB and more, panels of 128 columns
-// (512-byte segments in the strided host copies), at most eight.
-int host_panel_count(const csrspmm_b200_args* a)
+// Column panels of a host round trip over Nd columns: `requested` > 0 asks for that many, else
+// CSRSPMM_HOST_PANELS in the environment (1 = off), else the rule -- a B of 256 MiB and more with
+// Nd >= 256 goes in panels of 128 columns (512-byte segments in the strided host copies), at
+// most eight.  Widths are multiples of 32 columns except possibly the last.  Returns the count
+// and fills first[]/width[] (kMaxPanels entries each) when they are given.
+int column_panel_layout(int32_t Kd, int32_t Nd, int requested, int32_t* first, int32_t* width)
 {
-    int want = 0;
-    if (const char* e = std::getenv("CSRSPMM_HOST_PANELS")) want = std::atoi(e);
+    int want = requested;
+    if (want <= 0)
+        if (const char* e = std::getenv("CSRSPMM_HOST_PANELS")) want = std::atoi(e);
     if (want <= 0) {
-        const size_t b_bytes = (size_t)a->Kd * (size_t)a->Nd * 4;
-        want = (b_bytes >= ((size_t)256 << 20) && a->Nd >= 256) ? a->Nd / 128 : 1;
+        const size_t b_bytes = (size_t)Kd * (size_t)Nd * 4;
+        want = (b_bytes >= ((size_t)256 << 20) && Nd >= 256) ? Nd / 128 : 1;
         if (want > 8) want = 8;
     }
     if (want > kMaxPanels) want = kMaxPanels;
-    if (want > a->Nd / 32) want = a->Nd / 32;  // never narrower than 32 columns
-    return want < 1 ? 1 : want;
+    if (want > Nd / 32) want = Nd / 32;  // never narrower than 32 columns
+    if (want < 1) want = 1;
+    const int pw = want > 1 ? ((Nd + want - 1) / want + 31) / 32 * 32 : (Nd > 0 ? Nd : 1);
+    int count = 0;
+    for (int c0 = 0; c0 < Nd || count == 0; c0 += pw) {
+        if (first) first[count] = c0;
+        if (width) width[count] = (Nd - c0 < pw) ? (Nd - c0 > 0 ? Nd - c0 : 0) : pw;
+        ++count;
+    }
+    return count;
 }
 
 struct HostBuffers {
@@ -261,9 +272,8 @@ struct HostBuffers {
 
 int spmm_host_panels(const csrspmm_b200_args* a, const HostBuffers& d, int panels, cudaStream_t st, int* word)
 {
-    // panel width: a multiple of 32 columns, so every panel but the last keeps the vector layout
-    int pw = ((a->Nd + panels - 1) / panels + 31) / 32 * 32;
-    panels = (a->Nd + pw - 1) / pw;
+    int32_t first[kMaxPanels], width[kMaxPanels];
+    panels = column_panel_layout(a->Kd, a->Nd, panels, first, width);
 
     cudaStream_t compute = nullptr, out = nullptr;
     cudaEvent_t up[kMaxPanels] = {}, done[kMaxPanels] = {};
@@ -291,8 +301,7 @@ int spmm_host_panels(const csrspmm_b200_args* a, const HostBuffers& d, int panel
     for (; n_done < panels; ++n_done) CUDA_TRY_PANEL(cudaEventCreateWithFlags(&done[n_done], cudaEventDisableTiming));
 
     for (int q = 0; q < panels; ++q) {
-        const int c0 = q * pw;
-        const int w = (a->Nd - c0 < pw) ? a->Nd - c0 : pw;
+        const int c0 = first[q], w = width[q];
         float* dB = d.B + (size_t)a->Kd * (size_t)c0;
         float* dC = d.C + (size_t)a->M * (size_t)c0;
         if (a->beta != 0.0f)
@@ -448,7 +457,7 @@ int csrspmm_b200_spmm_host(const csrspmm_b200_args* a, void* device_arena, size_
     void* d_ws = cur; cur += align256(ws_bytes);
     int32_t* d_status = reinterpret_cast<int32_t*>(cur);
 
-    const int panels = host_panel_count(a);
+    const int panels = column_panel_layout(a->Kd, a->Nd, 0, nullptr, nullptr);
     if (panels > 1) {
         // A first, on the caller's stream; the panels of B follow it on the same stream
         int word = 0;
@@ -576,6 +585,12 @@ int csrspmm_b200_spmm_host(const csrspmm_b200_args* a, void* device_arena, size_
     }
     return CSRSPMM_B200_OK;
 #undef CUDA_TRY_HOST
+}
+
+int csrspmm_b200_column_panels(int32_t Kd, int32_t Nd, int requested, int32_t* first_col, int32_t* width)
+{
+    if (Kd < 0 || Nd < 0) return 0;
+    return column_panel_layout(Kd, Nd, requested, first_col, width);
 }
 
 int csrspmm_b200_copy_rows(void* dst, size_t dst_pitch_bytes, const void* src, size_t src_pitch_bytes,

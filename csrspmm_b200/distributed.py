@@ -102,14 +102,16 @@ def sum_over_ranks(value: float, device) -> float:
 
 
 def column_panels(Kd: int, Nd: int, panels: int | None = None):
-    """[(first column, width)] of the column panels a host round trip is cut into.  ``panels`` None
-    applies the library's rule (a B of 256 MiB or more with Nd >= 256: panels of 128 columns, at
-    most eight); widths are multiples of 32 columns except possibly the last."""
-    if panels is None:
-        panels = min(Nd // 128, 8) if (Kd * Nd * 4 >= (256 << 20) and Nd >= 256) else 1
-    panels = max(1, min(int(panels), 16, max(Nd // 32, 1)))
-    pw = ((Nd + panels - 1) // panels + 31) // 32 * 32 if panels > 1 else Nd
-    return [(c0, min(pw, Nd - c0)) for c0 in range(0, max(Nd, 1), max(pw, 1))] if Nd > 0 else [(0, 0)]
+    """[(first column, width)] of the column panels a host round trip is cut into, as the C library
+    lays them out.  ``panels`` None applies its rule (a B of 256 MiB or more with Nd >= 256: panels
+    of 128 columns, at most eight; CSRSPMM_HOST_PANELS in the environment overrides); widths are
+    multiples of 32 columns except possibly the last."""
+    first = np.zeros(16, np.int32)
+    width = np.zeros(16, np.int32)
+    n = _lib.lib().csrspmm_b200_column_panels(int(Kd), int(Nd), int(panels or 0), first.ctypes.data, width.ctypes.data)
+    if n < 1:
+        raise ValueError("csrspmm_b200_column_panels: negative size")
+    return [(int(first[k]), int(width[k])) for k in range(n)]
 
 
 class ShardedHostSpmm:

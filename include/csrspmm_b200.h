@@ -134,6 +134,13 @@ int csrspmm_b200_spmm_host(const csrspmm_b200_args* args, void* device_arena,
                            size_t device_arena_bytes, csrspmm_b200_stream_t stream);
 size_t csrspmm_b200_host_arena_bytes(const csrspmm_b200_args* args);
 
+/* No counterpart in the reference.  The column panels csrspmm_b200_spmm_host cuts a product of
+ * these sizes into: returns their number (1 = unsplit, at most CSRSPMM_B200_MAX_PANELS) and, when
+ * the arrays are given, each panel's first column and width.  requested > 0 asks for that many
+ * panels instead of the rule; widths are multiples of 32 columns except possibly the last. */
+#define CSRSPMM_B200_MAX_PANELS 16
+int csrspmm_b200_column_panels(int32_t Kd, int32_t Nd, int requested, int32_t* first_col, int32_t* width);
+
 /* No counterpart in the reference (its dense_host2device / dense_device2host,
  * src/host/dense_utils.cpp, copy whole packed matrices).  Asynchronous copy of `rows` rows of
  * `width_bytes` bytes between host and device, each side with its own pitch -- what a caller

@@ -208,3 +208,28 @@ def test_sweep_summary_matches_the_reference_summary_definition():
     s = {a: (g, sp) for a, g, sp in sweep.summarize(rows)}
     assert s["Naive"] == (200.0, 2.5) and s["cuSPARSE"] == (75.0, 1.0)
     assert len(sweep.SHAPES) == 4 and len(sweep.DENSITIES) == 5 and len(sweep.ENTRIES) == 5
+
+
+@pytest.mark.parametrize("Kd,Nd,panels", [(1 << 22, 512, None), (1 << 22, 500, 4), (1000, 64, None), (1 << 20, 256, None),
+                                         (1 << 22, 512, 40), (5, 33, 2), (7, 1, 3)])
+def test_column_panels_cover_the_width(Kd, Nd, panels):
+    """Host rule of the panelled round trip: panels tile [0, Nd) in order, widths are multiples of 32
+    columns except the last, never more than 16 panels; small operands stay in one piece."""
+    from csrspmm_b200.distributed import column_panels
+    ps = column_panels(Kd, Nd, panels)
+    assert 1 <= len(ps) <= 16
+    assert ps[0][0] == 0 and sum(w for _, w in ps) == Nd
+    for (c0, w), (c1, _) in zip(ps[:-1], ps[1:]):
+        assert c0 + w == c1 and w % 32 == 0 and w > 0
+    if panels is None and Kd * Nd * 4 < (256 << 20):
+        assert len(ps) == 1
+    if panels is None and Kd == 1 << 22 and Nd == 512:
+        assert ps == [(0, 128), (128, 128), (256, 128), (384, 128)]
+
+
+def test_copy_rows_rejects_bad_arguments_before_any_cuda_call():
+    L = _lib.lib()
+    buf = np.zeros(64, np.float32)
+    assert L.csrspmm_b200_copy_rows(None, 16, buf.ctypes.data, 16, 16, 4, 0, None) == _lib.ERR_BAD_ARG
+    assert L.csrspmm_b200_copy_rows(buf.ctypes.data, 8, buf.ctypes.data, 16, 16, 4, 0, None) == _lib.ERR_BAD_ARG
+    assert L.csrspmm_b200_copy_rows(None, 0, None, 0, 0, 4, 0, None) == _lib.OK  # nothing to copy
