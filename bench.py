@@ -460,7 +460,7 @@ def main(argv=None):
             n_panels = len(runner.panels)
             h2d, d2h, xchg = runner.h2d_bytes, runner.d2h_bytes, runner.exchange_bytes
             api = ("distributed.ShardedHostSpmm (per rank: pinned host block of A and 1/N of B in, NCCL all-gather of "
-                   f"B, host block of C out; {n_panels} column panel(s) pipelined over three streams)")
+                   f"B, host block of C out; {n_panels} column panel(s), the stages of different panels overlap)")
         torch.cuda.synchronize()
         e2e_step()  # warm-up
         barrier()

@@ -126,7 +126,7 @@ class ShardedHostSpmm:
     A wide product runs in column panels (``column_panels``): C[:, panel] needs B[:, panel] only,
     so while panel q is gathered and multiplied, panel q+1 of the B slice is still arriving over
     PCIe and panel q-1 of C is already leaving -- uploads, NVLink exchange, kernels and downloads of
-    different panels run at the same time on three streams.  On the device each panel of B and
+    different panels run at the same time, each stage on its own stream.  On the device each panel of B and
     of C is stored contiguously; every element of C is the same sum as in the unsplit product.
     """
 
@@ -159,8 +159,9 @@ class ShardedHostSpmm:
             ws = call._keep[5] if ws is None else ws
             self.calls.append(call)
         with torch.cuda.device(d):
-            self.s_up, self.s_mul, self.s_down = torch.cuda.Stream(d), torch.cuda.Stream(d), torch.cuda.Stream(d)
+            self.s_up, self.s_gather, self.s_mul, self.s_down = (torch.cuda.Stream(d) for _ in range(4))
             self.ev_up = [torch.cuda.Event() for _ in self.panels]
+            self.ev_gather = [torch.cuda.Event() for _ in self.panels]
             self.ev_mul = [torch.cuda.Event() for _ in self.panels]
         self.h2d_bytes = (rows + 1) * 4 + shard_host.nnz * 8 + self.slice_rows * Nd * 4
         self.d2h_bytes = rows * Nd * 4
@@ -178,17 +179,21 @@ class ShardedHostSpmm:
             with torch.cuda.stream(self.s_up):
                 self.ops.copy_rows(mine, self.h_B[:, c0:c0 + w])
                 self.ev_up[q].record()
-            with torch.cuda.stream(self.s_mul):
-                self.s_mul.wait_event(self.ev_up[q])
-                if self.world > 1:
+            ready = self.ev_up[q]
+            if self.world > 1:
+                with torch.cuda.stream(self.s_gather):
+                    self.s_gather.wait_event(self.ev_up[q])
                     self.dist.all_gather_into_tensor(self.d_B[q], mine)  # in place: slice g already sits at offset g
+                    self.ev_gather[q].record()
+                ready = self.ev_gather[q]
+            with torch.cuda.stream(self.s_mul):
+                self.s_mul.wait_event(ready)
                 self.calls[q]()
                 self.ev_mul[q].record()
             with torch.cuda.stream(self.s_down):
                 self.s_down.wait_event(self.ev_mul[q])
                 self.ops.copy_rows(self.C_host[:, c0:c0 + w], self.d_C[q])
-        self.s_mul.synchronize()
-        self.s_down.synchronize()
+        self.s_down.synchronize()  # the last download follows every other stage
         return self.C_host
 
 
