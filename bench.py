@@ -13,8 +13,9 @@ outside the timed region, and every rank multiplies its block: strong scaling, n
 the timed loop.  Rank 0 prints ONE JSON line.
 
   value / ms_per_step   device time, max over ranks, inputs resident in HBM
-  e2e                   the same product through csrspmm_b200_spmm_host: pinned HOST buffers in,
-                        host C out, copies inside the timed region
+  e2e                   the same product through csrspmm_b200_spmm_host (N > 1: through
+                        distributed.ShardedHostSpmm): pinned HOST buffers in, host C out, copies
+                        inside the timed region, pipelined over column panels (--e2e-panels)
   roofline              compulsory bytes of rank 0's block / its step time, against the measured
                         HBM copy bandwidth in MEASURED_PEAKS.json
   cpu_baseline          the CPU oracle (OpenMP over rows) on a bounded row sample, rank 0, N = 1
