@@ -156,7 +156,7 @@ class ShardedHostSpmm:
         for Bq, Cq in zip(self.d_B, self.d_C):  # widest panel first, so its scratch serves the others
             call = ops.SpmmCall(self.d_rp, self.d_ci, self.d_va, Bq, Cq, 1.0, 0.0, kernel=kernel,
                                 max_row_nnz=shard_host.max_row_nnz, workspace=ws)
-            ws = call._keep[5] if ws is None else ws
+            ws = call.workspace if ws is None else ws
             self.calls.append(call)
         with torch.cuda.device(d):
             self.s_up, self.s_gather, self.s_mul, self.s_down = (torch.cuda.Stream(d) for _ in range(4))

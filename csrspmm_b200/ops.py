@@ -157,6 +157,7 @@ class SpmmCall:
                     workspace = torch.empty(need, dtype=torch.uint8, device=B.device)
                 self.args.workspace = workspace.data_ptr()
                 self.args.workspace_bytes = workspace.numel() * workspace.element_size()
+        self.workspace = workspace  # scratch of the split kernels (None for the row kernel); may be shared
         self._keep = (row_ptr, col_idx, values, B, C_out, workspace, status_word)
         self._ref = C.byref(self.args)
         self.out = C_out

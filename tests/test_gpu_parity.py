@@ -622,3 +622,14 @@ def test_sharded_host_pipeline_single_rank(cuda_lib, panels):
         runner.C_host.fill_(float("nan"))
         got = runner.run()
         assert np.array_equal(got.numpy(), want)
+
+
+def test_host_round_trip_in_column_panels_pageable_memory(cuda_lib, monkeypatch):
+    """Host operands that are not pinned: the copies fall back to staged transfers, the result is the same."""
+    p = G.random_csr(2000, 1500, 256, 0.005, seed=33)
+    want = oracle.spmm(*arrays(p), threads=4)
+    h = [torch.from_numpy(x) for x in arrays(p)]
+    C_host = torch.empty(p.M, p.Nd)
+    monkeypatch.setenv("CSRSPMM_HOST_PANELS", "2")
+    ops.spmm_host(*h, C_host, max_row_nnz=int(np.diff(p.row_ptr).max()))
+    assert np.array_equal(C_host.numpy(), want)
