@@ -67,9 +67,21 @@ template <int NV, int FMT>
 cudaError_t launch_tma(const SpmmParams& p, const Plan& plan, cudaStream_t st)
 {
     auto kern = spmm_tma_kernel<NV, CSRSPMM_TUNE_TMA_TG, CSRSPMM_TUNE_TMA_SLOTS, FMT>;
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         (int)plan.dynamic_smem);
+    // The opt-in to more than 48 KB of dynamic shared memory is made once per device and
+    // instantiation, for the largest ring the kernel can ask for (rows of 2 KB), so that later
+    // calls -- inside a stream capture too -- are a plain launch.  Racing first calls repeat the
+    // same setting.
+    constexpr int kMaxRing = 8 * (CSRSPMM_TUNE_TMA_SLOTS * 2048 > 512 * NV ? CSRSPMM_TUNE_TMA_SLOTS * 2048 : 512 * NV);
+    static bool configured[64] = {};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return e;
+    if (dev < 0 || dev >= 64 || !configured[dev] || (int)plan.dynamic_smem > kMaxRing) {
+        const int want = (int)plan.dynamic_smem > kMaxRing ? (int)plan.dynamic_smem : kMaxRing;
+        e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, want);
+        if (e != cudaSuccess) return e;
+        if (dev >= 0 && dev < 64) configured[dev] = true;
+    }
     kern<<<(unsigned)plan.grid, kMergeThreads, plan.dynamic_smem, st>>>(p, (unsigned)plan.tma_slot_bytes,
                                                                         (unsigned)(plan.dynamic_smem / 8));
     return cudaSuccess;
