@@ -171,6 +171,51 @@ def time_spmm(torch, ops, t, C_out, workspace, kernel, steps, warmup, flush_buf,
     return total_ms / 1e3 / steps
 
 
+def launch_bound_modes(torch, ops, t, C_out, workspace, kernel, max_row_nnz, flush_buf, reps=100):
+    """A small product in the ways a caller can issue it, microseconds per launch over `reps` launches:
+    L2-cold (252 MiB written between launches; median and min of per-launch events), L2-warm back to
+    back (one event pair around all launches, launch gaps included), the same launches replayed from
+    one CUDA graph (launch gaps removed), and warm with beta = 0.5 (C read as well as written)."""
+    kw = dict(kernel=kernel, workspace=workspace, max_row_nnz=max_row_nnz)
+    step = ops.SpmmCall(t["row_ptr"], t["col_idx"], t["values"], t["B"], C_out, 1.0, 0.0, **kw)
+    step_beta = ops.SpmmCall(t["row_ptr"], t["col_idx"], t["values"], t["B"], C_out, 1.0, 0.5, **kw)
+    ev = lambda: torch.cuda.Event(enable_timing=True)  # noqa: E731
+
+    def back_to_back(fn):
+        for _ in range(10):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = ev(), ev()
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) * 1e3 / reps
+
+    out = {"launches": reps}
+    cold = []
+    for i in range(reps + 3):
+        flush_buf.zero_()
+        e0, e1 = ev(), ev()
+        e0.record()
+        step()
+        e1.record()
+        cold.append((e0, e1))
+    torch.cuda.synchronize()
+    cold = sorted(a.elapsed_time(b) * 1e3 for a, b in cold[3:])
+    out["cold_us_median"], out["cold_us_min"] = cold[len(cold) // 2], cold[0]
+    out["warm_us"] = back_to_back(step)
+    out["warm_beta_half_us"] = back_to_back(step_beta)
+    g, side = torch.cuda.CUDAGraph(), torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(g, stream=side):
+            for _ in range(reps):
+                step()
+    out["graph_us"] = back_to_back(g.replay) / reps
+    return out
+
+
 def problem_bytes(G, t, M, Nd, nnz, Kd, value_bytes=4.0):
     touched = G.touched_rows(t["col_idx"], Kd) if nnz else 0
     return G.min_bytes(M, Nd, nnz, touched, 0.0, value_bytes), touched
@@ -536,7 +581,7 @@ def main(argv=None):
 def other_workloads(torch, ops, G, ns, dev, peak):
     """Kernel-only numbers for the other BASELINE configs (1 GPU), each next to cuSPARSE."""
     out = {}
-    for name in ("cfg2_medium", "cfg3_powerlaw", "cfg4_fp4"):
+    for name in ("cfg1_check", "cfg2_medium", "cfg3_powerlaw", "cfg4_fp4"):
         if name == ns.workload:
             continue
         try:
@@ -556,6 +601,8 @@ def other_workloads(torch, ops, G, ns, dev, peak):
                                        "roofline_frac": nbytes / sec / 1e9 / peak}
             auto = ops.selected_kernel(p.M, p.Kd, p.Nd, p.nnz, max_row_nnz=mx)
             entry["auto"] = auto
+            if fb is not None and p.nnz < 1_000_000:  # launch-bound sizes: how the call is issued matters
+                entry["launch_modes_auto_kernel"] = launch_bound_modes(torch, ops, t, C_out, ws, auto, mx, fb)
             cs = cusparse_via_torch(torch, t, p.M, p.Kd, 20, 3, fb)
             entry["cusparse_torch"] = {"gflops": flops / cs / 1e9, "us": cs * 1e6} if isinstance(cs, float) else cs
             entry["cusparse"] = cusparse_summary(cusparse_direct(torch, t, p.M, p.Kd, p.Nd, p.nnz, C_out, 20, 3, fb), flops)
