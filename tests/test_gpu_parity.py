@@ -297,6 +297,43 @@ def test_cfg5_xl_eighth_size(cuda_lib, kernel):
     assert torch.equal(Cd, ops.spmm(p.row_ptr, p.col_idx, p.values, p.B, kernel=kernel, sync=True))
 
 
+def test_cfg5_xl_full_size(cuda_lib):
+    """BASELINE config 5 at full size (2^22 rows, 134 M nnz, B and C 8.6 GB each), AUTO kernel.  Oracle on a
+    row sample (random rows, the longest rows, the rows at the 8-GPU partition cuts); every row, long ones
+    included, through a B whose products can be summed independently on the device in fp64."""
+    from csrspmm_b200 import distributed as D
+    p = G.make("cfg5_xl", device="cuda")
+    assert p.M == 1 << 22 and p.Nd == 512 and abs(p.nnz / p.M - 32.0) < 0.2
+    rp_h = p.row_ptr.cpu().numpy()
+    assert ops.selected_kernel(p.M, p.Kd, p.Nd, p.nnz) == "tma"
+    Cd = ops.spmm(p.row_ptr, p.col_idx, p.values, p.B, sync=True)
+    cuts = D.partition_rows(rp_h, 8)[1:-1].astype(np.int64)
+    rows = np.concatenate([_sample(rp_h, np.random.default_rng(5), 4000, 4), cuts, cuts - 1])
+    rate = _check_sampled_rows(rp_h, p.col_idx, p.values, p.B, Cd, rows)
+    assert rate > 0.999
+    assert torch.equal(Cd, ops.spmm(p.row_ptr, p.col_idx, p.values, p.B, sync=True))  # fixed summation order
+    del Cd
+    # B2[k, c] = ((31 k + c) mod 13) - 6: small integers, so every product is exact and only the summation
+    # differs between the kernel (fp32, stored order) and torch (fp64 prefix sums)
+    k = torch.arange(p.Kd, device="cuda", dtype=torch.int64)[:, None]
+    c = torch.arange(p.Nd, device="cuda", dtype=torch.int64)[None, :]
+    B2 = (((31 * k + c) % 13) - 6).to(torch.float32)
+    C2 = ops.spmm(p.row_ptr, p.col_idx, p.values, B2, sync=True)
+    lo, hi = p.row_ptr[:-1].long(), p.row_ptr[1:].long()
+    for col in (0, 255, 511):
+        w = p.values.double() * B2[p.col_idx.long(), col].double()
+        acc = torch.zeros(p.nnz + 1, dtype=torch.float64, device="cuda")
+        acc[1:] = torch.cumsum(w, 0)
+        mag = torch.zeros(p.nnz + 1, dtype=torch.float64, device="cuda")
+        mag[1:] = torch.cumsum(w.abs(), 0)
+        want, bound = acc[hi] - acc[lo], mag[hi] - mag[lo]
+        err = (C2[:, col].double() - want).abs()
+        # fp32 summation of n terms: error about sqrt(n) * 6e-8 * sum|terms| (n up to 65 536 here); a wrong
+        # or missing B row would show up at the size of the bound itself
+        assert bool((err <= 1e-4 * bound + 1e-3).all()), float((err - 1e-4 * bound).max())
+        del w, acc, mag
+
+
 # ---- e2m1 values -----------------------------------------------------------------------------------
 
 @pytest.mark.parametrize("kernel", KERNELS)
