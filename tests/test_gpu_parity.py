@@ -297,6 +297,23 @@ def test_cfg5_xl_eighth_size(cuda_lib, kernel):
     assert torch.equal(Cd, ops.spmm(p.row_ptr, p.col_idx, p.values, p.B, kernel=kernel, sync=True))
 
 
+def test_cfg4_fp4_full_size(cuda_lib):
+    """BASELINE config 4 at full size (65 536 rows of about 328, Nd 256) against the oracle on every row:
+    the AUTO choice (whole-row kernel) bit for bit, with fp32 values and with packed e2m1 values."""
+    p = G.make("cfg4_fp4")
+    mx = int(np.diff(p.row_ptr).max())
+    assert p.nnz > 21_000_000 and ops.selected_kernel(p.M, p.Kd, p.Nd, p.nnz, max_row_nnz=mx) == "row"
+    t = [dev(x) for x in arrays(p)]
+    want = oracle.spmm(*arrays(p), fused=True, threads=oracle.max_threads())
+    got = ops.spmm(*t, max_row_nnz=mx, sync=True).cpu().numpy()
+    assert np.array_equal(got, want)
+    packed, scale = ops.e2m1_quantize(p.values)
+    decoded = oracle.e2m1_decode(packed.numpy(), p.nnz, scale)
+    want4 = oracle.spmm(p.row_ptr, p.col_idx, decoded, p.B, fused=True, threads=oracle.max_threads())
+    got4 = ops.spmm(t[0], t[1], packed.cuda(), t[3], max_row_nnz=mx, e2m1_scale=scale, nnz=p.nnz, sync=True).cpu().numpy()
+    assert np.array_equal(got4, want4)
+
+
 def test_cfg5_xl_full_size(cuda_lib):
     """BASELINE config 5 at full size (2^22 rows, 134 M nnz, B and C 8.6 GB each), AUTO kernel.  Oracle on a
     row sample (random rows, the longest rows, the rows at the 8-GPU partition cuts); every row, long ones
