@@ -636,11 +636,11 @@ def test_host_round_trip_in_column_panels(cuda_lib, monkeypatch, panels, Nd):
 
 
 def test_host_round_trip_in_column_panels_split_rows(cuda_lib, monkeypatch):
-    """Column panels on a skewed matrix (merge-path kernel inside each panel)."""
-    p = G.make("cfg3_powerlaw", scale=32, Nd=256)
+    """Column panels on a skewed matrix (merge-path kernel inside each panel, 64 MiB of C per panel)."""
+    p = G.make("cfg3_powerlaw", scale=8, Nd=256)
     h = [torch.from_numpy(x).pin_memory() for x in arrays(p)]
-    C_host = torch.empty(p.M, p.Nd).pin_memory()
-    monkeypatch.setenv("CSRSPMM_HOST_PANELS", "4")
+    C_host = torch.full((p.M, p.Nd), float("nan")).pin_memory()
+    monkeypatch.setenv("CSRSPMM_HOST_PANELS", "2")
     ops.spmm_host(*h, C_host)
     f64, mag = oracle.spmm_f64(p.row_ptr, p.col_idx, p.values, p.B, threads=4)
     assert (np.abs(C_host.numpy() - f64) <= RTOL * mag + ATOL).all()
