@@ -5,8 +5,8 @@
 // hosts of this library can do neither: a process whose own memory manager claimed the whole
 // device at start-up (a later cudaMalloc or pool allocation fails, or comes back after a
 // device-wide synchronisation it cannot afford), a plug-in called from inside somebody else's
-// runtime that forbids allocation calls on its threads, or a control loop with a hard latency
-// budget that must never enter the allocator.  Such a caller already owns A, B and C; the only
+// runtime that forbids allocation calls on its threads, or a control loop with a hard deadline
+// per call that must never enter the allocator.  Such a caller already owns A, B and C; the only
 // thing it cannot provide on the spot is the scratch.  This entry point therefore carries a fixed
 // scratch array in the library's device image and calls no allocation routine of any kind.
 //
