@@ -121,6 +121,47 @@ def spmm(row_ptr, col_idx, values, B, C_out=None, alpha=1.0, beta=0.0, *, entry=
     return C_out
 
 
+def spmm_tiled(row_ptr, col_idx, values, B, C_out=None, alpha=1.0, beta=0.0, *, panel_rows=0, e2m1_scale=None,
+               nnz=None, workspace=None, status_word=None):
+    """The same product as ``spmm`` in passes over column panels of A whose slab of B (``panel_rows`` rows;
+    0 = the library's 64 MiB choice) stays in L2 (``csrspmm_b200_spmm_tiled``).  Opt-in: it pays when rows
+    hold several non-zeros per panel and B is several times L2.  Bit-identical to the whole-row kernel."""
+    packed = e2m1_scale is not None
+    _check_csr(row_ptr, col_idx, values, B, packed)
+    M, Kd, Nd = row_ptr.numel() - 1, B.size(0), B.size(1)
+    n = int(col_idx.numel() if nnz is None else nnz)
+    if C_out is None:
+        if beta != 0.0:
+            raise RuntimeError("beta != 0 needs C_out")
+        C_out = torch.empty((M, Nd), dtype=torch.float32, device=B.device)
+    elif not C_out.is_cuda or C_out.dtype != torch.float32 or C_out.shape != (M, Nd) or C_out.device != B.device:
+        raise RuntimeError("C_out must be a float32 CUDA tensor of shape (M, Nd) on B's device")
+    L = _lib.lib()
+    a = _lib.make_args(M, Kd, Nd, n, row_ptr.data_ptr(), col_idx.data_ptr(), values.data_ptr(), B.data_ptr(),
+                       C_out.data_ptr(), ldb=max(B.stride(0) if Kd > 1 else Nd, Nd),
+                       ldc=max(C_out.stride(0) if M > 1 else Nd, Nd), alpha=alpha, beta=beta,
+                       value_format=_lib.VALUES_E2M1 if packed else _lib.VALUES_F32,
+                       value_scale=float(e2m1_scale) if packed else 1.0,
+                       status_word=status_word.data_ptr() if status_word is not None else 0)
+    with torch.cuda.device(B.device):
+        need = int(L.csrspmm_b200_tiled_workspace_bytes(C.byref(a)))
+        if workspace is None or workspace.numel() * workspace.element_size() < need:
+            workspace = torch.empty(max(need, 256), dtype=torch.uint8, device=B.device)
+        a.workspace = workspace.data_ptr()
+        a.workspace_bytes = workspace.numel() * workspace.element_size()
+        stream = torch.cuda.current_stream(B.device)
+        _lib.check(L.csrspmm_b200_spmm_tiled(C.byref(a), int(panel_rows), C.c_void_p(stream.cuda_stream)),
+                   "csrspmm_b200_spmm_tiled")
+        workspace.record_stream(stream)
+    return C_out
+
+
+def tiled_panel_rows(Kd: int, Nd: int, ldb: int | None = None) -> int:
+    """Rows of B per panel that ``spmm_tiled`` chooses by itself (0: B is no larger than one slab)."""
+    a = _lib.make_args(1, Kd, Nd, 0, ldb=ldb or Nd)
+    return int(_lib.lib().csrspmm_b200_tiled_panel_rows(C.byref(a)))
+
+
 class SpmmCall:
     """A prepared SpMM: argument block, kernel choice and scratch fixed once, so that each call is
     a single trip through the C ABI.  For tight launch loops (benchmarks, repeated products with the

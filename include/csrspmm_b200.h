@@ -164,6 +164,25 @@ int csrspmm_b200_copy_rows(void* dst, size_t dst_pitch_bytes, const void* src, s
 #define CSRSPMM_B200_NOALLOC_SCRATCH_BYTES (8u << 20)
 int csrspmm_b200_spmm_noalloc(const csrspmm_b200_args* args, csrspmm_b200_stream_t stream);
 
+/* No counterpart in the reference (a locality pass for operands far larger than L2).  The same
+ * product as csrspmm_b200_spmm, computed in passes over panels of `panel_rows` columns of A (= rows
+ * of B), so that each slab of B is read from HBM once and then served from L2: pass t takes, for
+ * every row, the stored entries from where pass t-1 stopped up to the first one whose column index
+ * is not below (t+1)*panel_rows.  Each pass re-reads and re-writes the running sums of the rows
+ * it touches; on B200 that cost has so far matched or exceeded the HBM traffic saved (level with
+ * csrspmm_b200_spmm at best, on long even rows and a B of several times L2; slower elsewhere), so
+ * AUTO never picks it and it stays an explicit choice.  Columns need not be sorted
+ * (sorted columns give each pass exactly its panel).  Every output accumulates its products in
+ * stored order, so the result is bit-identical to the whole-row kernel's.  Device pointers;
+ * args.kernel is ignored; args.workspace (256-byte aligned, csrspmm_b200_tiled_workspace_bytes
+ * bytes: one int32 per row, plus M x Nd floats when beta != 0) or NULL to let the call take it
+ * from cudaMallocAsync.  panel_rows = 0 asks for the library's choice
+ * (csrspmm_b200_tiled_panel_rows: a slab of 64 MiB; 0 when B is not larger than that, in which
+ * case the call is a single whole-row pass). */
+int32_t csrspmm_b200_tiled_panel_rows(const csrspmm_b200_args* args);
+size_t csrspmm_b200_tiled_workspace_bytes(const csrspmm_b200_args* args);
+int csrspmm_b200_spmm_tiled(const csrspmm_b200_args* args, int32_t panel_rows, csrspmm_b200_stream_t stream);
+
 /* Scratch the split kernels need for this problem (0 for the row kernel).  Depends only on
  * sizes, never on matrix contents. */
 size_t csrspmm_b200_workspace_bytes(const csrspmm_b200_args* args);

@@ -18,7 +18,7 @@ def test_library_loads_and_exports_every_declared_symbol():
     L = _lib.lib()
     assert L.csrspmm_b200_abi_version() == 1
     header = (ROOT / "include" / "csrspmm_b200.h").read_text()
-    declared = set(re.findall(r"^(?:int|size_t|float|const char\*)\s+(csrspmm_b200_[a-z0-9_]+)\(", header, re.M))
+    declared = set(re.findall(r"^(?:int|int32_t|size_t|float|const char\*)\s+(csrspmm_b200_[a-z0-9_]+)\(", header, re.M))
     assert declared == set(_lib.EXPORTED_SYMBOLS)
     for name in declared:
         assert hasattr(L, name), name
