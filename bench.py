@@ -623,32 +623,37 @@ def other_workloads(torch, ops, G, ns, dev, peak):
             torch.cuda.empty_cache()
         except Exception as e:  # secondary numbers must not take the headline down
             out[name] = f"failed: {type(e).__name__}: {e}"[:300]
-    out["long_rows_wide_B"] = locality_pass_case(torch, ops, G, dev)
+    out["long_rows_wide_B"] = locality_pass_case(torch, ops, G, dev, skewed=False)
+    out["long_skewed_rows_wide_B"] = locality_pass_case(torch, ops, G, dev, skewed=True)
     return out
 
 
-def locality_pass_case(torch, ops, G, dev):
+def locality_pass_case(torch, ops, G, dev, skewed):
     """The opt-in tiled product (csrspmm_b200_spmm_tiled) next to the untiled kernels where it has its best
-    chance: 65 536 rows of 328 non-zeros (ascending uniform columns) over Kd = 2^21, Nd = 256, so B is 2 GiB."""
+    chance: 65 536 rows of 328 non-zeros (ascending uniform columns) over Kd = 2^21, Nd = 256, so B is 2 GiB;
+    `skewed` draws the row lengths from Zipf(2) with the same mean instead (longest row 16 384)."""
     try:
         M, Kd, Nd, per = 65536, 1 << 21, 256, 328
         gen = torch.Generator(device=dev)
         gen.manual_seed(0)
-        lens = np.full(M, per, np.int64)
+        lens = (G.zipf_lengths(np.random.default_rng(0), M, Kd, 2.0, float(per), 16384) if skewed
+                else np.full(M, per, np.int64))
         rp = np.zeros(M + 1, np.int32)
         np.cumsum(lens, out=rp[1:])
         ci = G._columns_torch(gen, lens, Kd, dev)
-        va = torch.empty(M * per, device=dev).uniform_(-1.0, 1.0, generator=gen)
+        nnz = int(rp[-1])
+        va = torch.empty(nnz, device=dev).uniform_(-1.0, 1.0, generator=gen)
         B = torch.randn((Kd, Nd), device=dev, generator=gen)
         rp = torch.from_numpy(rp).to(dev)
         C_out = torch.empty((M, Nd), device=dev)
-        ws = torch.empty(ops.workspace_bytes(M, Kd, Nd, M * per) + 4 * M + 4096, dtype=torch.uint8, device=dev)
+        ws = torch.empty(ops.workspace_bytes(M, Kd, Nd, nnz) + 4 * M + 4096, dtype=torch.uint8, device=dev)
+        mx = int(lens.max())
         t = {"row_ptr": rp, "col_idx": ci, "values": va, "B": B}
-        res = {"M": M, "Kd": Kd, "Nd": Nd, "nnz": M * per, "B_bytes": Kd * Nd * 4, "us": {}}
+        res = {"M": M, "Kd": Kd, "Nd": Nd, "nnz": nnz, "max_row_nnz": mx, "B_bytes": Kd * Nd * 4, "us": {}}
         for k in ("row", "merge"):
-            res["us"][k] = time_spmm(torch, ops, t, C_out, ws, k, 5, 2, None, max_row_nnz=per) * 1e6
-        ref = ops.spmm(rp, ci, va, B, kernel="row", max_row_nnz=per, sync=True)
-        for slab_mib in (32, 64, 96):
+            res["us"][k] = time_spmm(torch, ops, t, C_out, ws, k, 5, 2, None, max_row_nnz=mx) * 1e6
+        ref = ops.spmm(rp, ci, va, B, kernel="row", max_row_nnz=mx, sync=True)
+        for slab_mib in ((64,) if skewed else (32, 64, 96)):
             pr = (slab_mib << 20) // (Nd * 4)
             for _ in range(2):
                 ops.spmm_tiled(rp, ci, va, B, C_out, panel_rows=pr, workspace=ws)
