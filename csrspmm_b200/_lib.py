@@ -36,6 +36,7 @@ EXPORTED_SYMBOLS = (
     "csrspmm_b200_row_stats_device", "csrspmm_b200_partition_rows", "csrspmm_b200_e2m1_scale",
     "csrspmm_b200_e2m1_encode", "csrspmm_b200_e2m1_decode", "csrspmm_b200_dense2csr_count",
     "csrspmm_b200_dense2csr_fill", "csrspmm_b200_csr2dense", "csrspmm_b200_copy_rows", "csrspmm_b200_column_panels",
+    "csrspmm_b200_e2m1_scale_device", "csrspmm_b200_e2m1_encode_device", "csrspmm_b200_e2m1_decode_device",
     "csrspmm_b200_spmm_tiled", "csrspmm_b200_tiled_workspace_bytes", "csrspmm_b200_tiled_panel_rows",
 )
 
@@ -104,6 +105,12 @@ def lib() -> C.CDLL:
         fn.restype = C.c_int
     L.csrspmm_b200_spmm_host.argtypes = [C.POINTER(Args), C.c_void_p, C.c_size_t, C.c_void_p]
     L.csrspmm_b200_spmm_host.restype = C.c_int
+    L.csrspmm_b200_e2m1_scale_device.argtypes = [C.c_int64, C.c_void_p, C.POINTER(C.c_float), C.c_void_p]
+    L.csrspmm_b200_e2m1_scale_device.restype = C.c_int
+    L.csrspmm_b200_e2m1_encode_device.argtypes = [C.c_int64, C.c_void_p, C.c_float, C.c_void_p, C.c_void_p]
+    L.csrspmm_b200_e2m1_encode_device.restype = C.c_int
+    L.csrspmm_b200_e2m1_decode_device.argtypes = [C.c_int64, C.c_void_p, C.c_float, C.c_void_p, C.c_void_p]
+    L.csrspmm_b200_e2m1_decode_device.restype = C.c_int
     L.csrspmm_b200_spmm_tiled.argtypes = [C.POINTER(Args), C.c_int32, C.c_void_p]
     L.csrspmm_b200_spmm_tiled.restype = C.c_int
     L.csrspmm_b200_tiled_workspace_bytes.argtypes = [C.POINTER(Args)]

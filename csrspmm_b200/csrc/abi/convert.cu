@@ -3,6 +3,9 @@
 // (src/host/csr_utils.cpp:70-145); results are identical, the matrices stay on the device.
 #include <cuda_runtime.h>
 
+#include <cstring>
+
+#include "../kernels/codec_kernels.cuh"
 #include "../kernels/convert_kernels.cuh"
 #include "csrspmm_b200.h"
 #include "plan.h"
@@ -86,6 +89,65 @@ int csrspmm_b200_csr2dense(int32_t H, int32_t W, const int32_t* row_ptr, const i
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
     CUDA_TRY(cudaMemset2DAsync(dense, (size_t)ld * 4, 0, (size_t)W * 4, (size_t)H, st));
     csr_scatter_kernel<<<(unsigned)(((long long)H + 7) / 8), 256, 0, st>>>(H, W, row_ptr, col_idx, values, dense, ld);
+    CUDA_TRY(cudaGetLastError());
+    return CSRSPMM_B200_OK;
+}
+
+// ---- e2m1 codec on the device ------------------------------------------------------------------
+
+int csrspmm_b200_e2m1_scale_device(int64_t n, const float* values, float* scale_out, csrspmm_b200_stream_t stream)
+{
+    if (n < 0 || scale_out == nullptr || (n > 0 && values == nullptr)) {
+        set_last_error("e2m1_scale_device: bad argument");
+        return CSRSPMM_B200_ERR_BAD_ARG;
+    }
+    *scale_out = 1.0f;
+    if (n == 0) return CSRSPMM_B200_OK;
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    unsigned* d_bits = nullptr;
+    CUDA_TRY(cudaMallocAsync(reinterpret_cast<void**>(&d_bits), sizeof(unsigned), st));
+    CUDA_TRY(cudaMemsetAsync(d_bits, 0, sizeof(unsigned), st));
+    const long long want = (n + 255) / 256;
+    const unsigned grid = (unsigned)(want < 148 * 16 ? want : 148 * 16);
+    e2m1_absmax_kernel<<<grid, 256, 0, st>>>(n, values, d_bits);
+    CUDA_TRY(cudaGetLastError());
+    unsigned bits = 0;
+    CUDA_TRY(cudaMemcpyAsync(&bits, d_bits, sizeof(unsigned), cudaMemcpyDeviceToHost, st));
+    CUDA_TRY(cudaFreeAsync(d_bits, st));
+    CUDA_TRY(cudaStreamSynchronize(st));
+    float mx;
+    static_assert(sizeof(mx) == sizeof(bits), "float is 32 bits");
+    memcpy(&mx, &bits, sizeof(mx));
+    *scale_out = mx > 0.0f ? mx / 6.0f : 1.0f;
+    return CSRSPMM_B200_OK;
+}
+
+int csrspmm_b200_e2m1_encode_device(int64_t n, const float* values, float scale, uint8_t* packed,
+                                    csrspmm_b200_stream_t stream)
+{
+    if (n < 0 || (n > 0 && (values == nullptr || packed == nullptr)) || !(scale > 0.0f)) {
+        set_last_error("e2m1_encode_device: bad argument");
+        return CSRSPMM_B200_ERR_BAD_ARG;
+    }
+    if (n == 0) return CSRSPMM_B200_OK;
+    const long long want = ((n + 1) / 2 + 255) / 256;
+    const unsigned grid = (unsigned)(want < 148 * 16 ? want : 148 * 16);
+    e2m1_encode_kernel<<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(n, values, scale, packed);
+    CUDA_TRY(cudaGetLastError());
+    return CSRSPMM_B200_OK;
+}
+
+int csrspmm_b200_e2m1_decode_device(int64_t n, const uint8_t* packed, float scale, float* values,
+                                    csrspmm_b200_stream_t stream)
+{
+    if (n < 0 || (n > 0 && (values == nullptr || packed == nullptr))) {
+        set_last_error("e2m1_decode_device: bad argument");
+        return CSRSPMM_B200_ERR_BAD_ARG;
+    }
+    if (n == 0) return CSRSPMM_B200_OK;
+    const long long want = (n + 255) / 256;
+    const unsigned grid = (unsigned)(want < 148 * 16 ? want : 148 * 16);
+    e2m1_decode_kernel<<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(n, packed, scale, values);
     CUDA_TRY(cudaGetLastError());
     return CSRSPMM_B200_OK;
 }

@@ -274,8 +274,21 @@ def csrspmm_warp_per_row_smem_fp4(A_rowptr, A_colidx, A_values, A_max_row_nnz, B
 # ---- helpers over the host-only / utility entry points -----------------------------------------------
 
 def e2m1_quantize(values_f32):
-    """Host fp32 tensor/array -> (packed uint8 CPU tensor, scale) with the library's codec."""
+    """fp32 tensor/array -> (packed uint8 tensor, scale) with the library's codec.  A CUDA tensor is
+    encoded on its device and the packed tensor stays there; anything else is encoded on the host."""
     import numpy as np
+    if isinstance(values_f32, torch.Tensor) and values_f32.is_cuda:
+        v = values_f32.detach().to(torch.float32).contiguous()
+        n = v.numel()
+        L = _lib.lib()
+        scale = C.c_float(1.0)
+        packed = torch.empty((n + 1) // 2, dtype=torch.uint8, device=v.device)
+        with torch.cuda.device(v.device):
+            st = C.c_void_p(torch.cuda.current_stream(v.device).cuda_stream)
+            _lib.check(L.csrspmm_b200_e2m1_scale_device(n, v.data_ptr(), C.byref(scale), st), "e2m1_scale_device")
+            _lib.check(L.csrspmm_b200_e2m1_encode_device(n, v.data_ptr(), scale.value, packed.data_ptr(), st),
+                       "e2m1_encode_device")
+        return packed, float(scale.value)
     v = np.ascontiguousarray(values_f32.detach().cpu().numpy() if isinstance(values_f32, torch.Tensor)
                              else values_f32, dtype=np.float32)
     L = _lib.lib()
@@ -286,7 +299,15 @@ def e2m1_quantize(values_f32):
 
 
 def e2m1_dequantize(packed, n, scale):
+    """Packed codes -> fp32 values (on the device for a CUDA tensor, else on the host)."""
     import numpy as np
+    if isinstance(packed, torch.Tensor) and packed.is_cuda:
+        out = torch.empty(int(n), dtype=torch.float32, device=packed.device)
+        with torch.cuda.device(packed.device):
+            st = C.c_void_p(torch.cuda.current_stream(packed.device).cuda_stream)
+            _lib.check(_lib.lib().csrspmm_b200_e2m1_decode_device(int(n), packed.contiguous().data_ptr(), float(scale),
+                                                                  out.data_ptr(), st), "e2m1_decode_device")
+        return out
     pk = np.ascontiguousarray(packed.cpu().numpy() if isinstance(packed, torch.Tensor) else packed, dtype=np.uint8)
     out = np.empty(int(n), np.float32)
     _lib.check(_lib.lib().csrspmm_b200_e2m1_decode(int(n), pk.ctypes.data, float(scale), out.ctypes.data),

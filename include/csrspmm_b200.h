@@ -245,6 +245,13 @@ int csrspmm_b200_partition_rows(int32_t M, const int32_t* row_ptr, int32_t parts
 float csrspmm_b200_e2m1_scale(int64_t n, const float* values);
 int csrspmm_b200_e2m1_encode(int64_t n, const float* values, float scale, uint8_t* packed);
 int csrspmm_b200_e2m1_decode(int64_t n, const uint8_t* packed, float scale, float* values);
+/* The same codec for arrays in device memory (same codes bit for bit).  _scale_device waits for the
+ * stream and writes the scale to host memory; _encode_device and _decode_device are asynchronous. */
+int csrspmm_b200_e2m1_scale_device(int64_t n, const float* values, float* scale_out, csrspmm_b200_stream_t stream);
+int csrspmm_b200_e2m1_encode_device(int64_t n, const float* values, float scale, uint8_t* packed,
+                                    csrspmm_b200_stream_t stream);
+int csrspmm_b200_e2m1_decode_device(int64_t n, const uint8_t* packed, float scale, float* values,
+                                    csrspmm_b200_stream_t stream);
 
 #ifdef __cplusplus
 }

@@ -54,3 +54,31 @@ def test_csr2dense_repeated_column_keeps_last_value(cuda_lib):
     va = torch.tensor([1.0, 5.0, 7.0], device="cuda")
     out = ops.csr2dense(rp, ci, va, (2, 4)).cpu().numpy()
     assert out.tolist() == [[5.0, 0.0, 7.0, 0.0], [0.0, 0.0, 0.0, 0.0]]
+
+
+def test_e2m1_device_codec_equals_host_codec(cuda_lib):
+    """Scale, codes and decoded values of the device codec equal the host codec's bit for bit: random values,
+    exact ties at every midpoint, saturation, signed zeros, NaN, an odd element count."""
+    rng = np.random.default_rng(12)
+    mids = np.array([0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0], np.float32)
+    special = np.concatenate([mids, -mids, np.nextafter(mids, np.float32(0)), np.nextafter(mids, np.float32(9)),
+                              [0.0, -0.0, 6.0, -6.0, 5.999, np.nan, 1e-30, -1e-30]]).astype(np.float32)
+    # the largest magnitude is 6, so scale is exactly 1 and the special values sit exactly on the ties
+    v = np.concatenate([special, rng.uniform(-6.0, 6.0, 100_001).astype(np.float32)])
+    assert v.shape[0] % 2 == 1
+    h_packed, h_scale = ops.e2m1_quantize(v)
+    d_packed, d_scale = ops.e2m1_quantize(torch.from_numpy(v).cuda())
+    assert d_packed.is_cuda and d_scale == h_scale == 1.0
+    assert torch.equal(d_packed.cpu(), h_packed)
+    h_dec = ops.e2m1_dequantize(h_packed, v.shape[0], h_scale)
+    d_dec = ops.e2m1_dequantize(d_packed, v.shape[0], d_scale)
+    assert d_dec.is_cuda and np.array_equal(d_dec.cpu().numpy().view(np.uint32), h_dec.numpy().view(np.uint32))
+    # a scale that is not a power of two, all-zero input, empty input
+    w = rng.standard_normal(4097).astype(np.float32) * 3.3
+    hp, hs = ops.e2m1_quantize(w)
+    dp, ds = ops.e2m1_quantize(torch.from_numpy(w).cuda())
+    assert ds == hs and torch.equal(dp.cpu(), hp)
+    zp, zs = ops.e2m1_quantize(torch.zeros(10, device="cuda"))
+    assert zs == 1.0 and int(zp.sum()) == 0
+    ep, es = ops.e2m1_quantize(torch.zeros(0, device="cuda"))
+    assert ep.numel() == 0 and es == 1.0
