@@ -95,7 +95,13 @@ def _f32(a) -> np.ndarray:
 
 
 def max_threads() -> int:
-    return int(lib().oracle_max_threads())
+    """Host threads the oracle may use: the cores this process is allowed on.  Not OpenMP's own default,
+    which a launcher may have capped through OMP_NUM_THREADS (torch.distributed.run sets it to 1); the
+    parallel regions take their thread count explicitly, so the cap does not apply to them."""
+    try:
+        return max(len(os.sched_getaffinity(0)), 1)
+    except AttributeError:
+        return max(os.cpu_count() or 1, int(lib().oracle_max_threads()))
 
 
 def spmm(row_ptr, col_idx, values, B, C_in=None, alpha=1.0, beta=0.0, *, fused=True, ncols=None,
