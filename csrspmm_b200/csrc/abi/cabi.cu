@@ -56,11 +56,16 @@ template <int S, int VW, int FMT>
 void launch_merge(const SpmmParams& p, const Plan& plan, cudaStream_t st)
 {
     constexpr int G = kShapes[S].G, NV = kShapes[S].NV, TG = kShapes[S].TG;
+    constexpr int TGS = CSRSPMM_TUNE_MERGE_TG_SMALL < TG ? CSRSPMM_TUNE_MERGE_TG_SMALL : TG;
     constexpr int U = VW == 1 ? 8 : merge_unroll(NV);
-    if (VW == 4 && plan.full)
-        spmm_merge_kernel<G, NV, VW, TG, U, FMT, (VW == 4)><<<(unsigned)plan.grid, kMergeThreads, 0, st>>>(p);
-    else
-        spmm_merge_kernel<G, NV, VW, TG, U, FMT, false><<<(unsigned)plan.grid, kMergeThreads, 0, st>>>(p);
+    const unsigned grid = (unsigned)plan.grid;
+    if (plan.small_tile) {  // few items: smaller tiles, more CTAs
+        if (VW == 4 && plan.full) spmm_merge_kernel<G, NV, VW, TGS, U, FMT, (VW == 4)><<<grid, kMergeThreads, 0, st>>>(p);
+        else spmm_merge_kernel<G, NV, VW, TGS, U, FMT, false><<<grid, kMergeThreads, 0, st>>>(p);
+    } else {
+        if (VW == 4 && plan.full) spmm_merge_kernel<G, NV, VW, TG, U, FMT, (VW == 4)><<<grid, kMergeThreads, 0, st>>>(p);
+        else spmm_merge_kernel<G, NV, VW, TG, U, FMT, false><<<grid, kMergeThreads, 0, st>>>(p);
+    }
 }
 
 template <int NV, int FMT>

@@ -13,7 +13,7 @@
 // Limits and rules.
 //   * The array is CSRSPMM_B200_NOALLOC_SCRATCH_BYTES (8 MiB) per device and exists on every GPU
 //     that loads the library, until the process ends.  A problem that needs more (one int32 plus
-//     one row of Nd floats per 1024 or 2048 merge-path items) is refused with ERR_WORKSPACE and a
+//     one row of Nd floats per 1536 to 3072 merge-path items) is refused with ERR_WORKSPACE and a
 //     message that states both numbers; nothing is launched.
 //   * It always runs the merge-path kernel (args.kernel, args.workspace, args.workspace_bytes
 //     are ignored).
@@ -78,8 +78,10 @@ template <int S, int VW, int FMT>
 void launch_one(const SpmmParams& p, const Plan& plan, cudaStream_t st)
 {
     constexpr int G = kShapes[S].G, NV = kShapes[S].NV, TG = kShapes[S].TG;
+    constexpr int TGS = CSRSPMM_TUNE_MERGE_TG_SMALL < TG ? CSRSPMM_TUNE_MERGE_TG_SMALL : TG;
     constexpr int U = VW == 1 ? 8 : merge_unroll(NV);
-    spmm_merge_kernel<G, NV, VW, TG, U, FMT, false><<<(unsigned)plan.grid, kMergeThreads, 0, st>>>(p);
+    if (plan.small_tile) spmm_merge_kernel<G, NV, VW, TGS, U, FMT, false><<<(unsigned)plan.grid, kMergeThreads, 0, st>>>(p);
+    else spmm_merge_kernel<G, NV, VW, TG, U, FMT, false><<<(unsigned)plan.grid, kMergeThreads, 0, st>>>(p);
 }
 
 template <int VW, int FMT>

@@ -115,6 +115,16 @@ static int forced_kernel_from_env()
     return CSRSPMM_B200_KERNEL_AUTO;
 }
 
+int merge_tile_for(int shape, long long num_items, bool* small)
+{
+    const int groups = 256 / kShapes[shape].G;
+    const int big = groups * kShapes[shape].TG;
+    const bool use_small = CSRSPMM_TUNE_MERGE_TG_SMALL < kShapes[shape].TG &&
+                           num_items < (long long)big * 148 * CSRSPMM_TUNE_MERGE_SMALL_BELOW_CTAS_PER_SM;
+    if (small != nullptr) *small = use_small;
+    return use_small ? groups * CSRSPMM_TUNE_MERGE_TG_SMALL : big;
+}
+
 static void fill_split_geometry(const csrspmm_b200_args* a, Plan* plan, int tile)
 {
     plan->tile = tile;
@@ -187,7 +197,7 @@ int make_plan(const csrspmm_b200_args* a, Plan* plan)
         plan->NV = kShapes[plan->shape].NV;
         plan->full = plan->VW == 4 && plan->G * plan->NV == plan->ncolv;
         if (kernel == CSRSPMM_B200_KERNEL_MERGE) {
-            fill_split_geometry(a, plan, (256 / plan->G) * kShapes[plan->shape].TG);
+            fill_split_geometry(a, plan, merge_tile_for(plan->shape, plan->num_items, &plan->small_tile));
         } else {
             const int groups = CSRSPMM_TUNE_ROW_THREADS / plan->G;
             plan->grid = ((long long)a->M + groups - 1) / groups;
@@ -214,7 +224,7 @@ size_t worst_case_workspace(const csrspmm_b200_args* a)
     // sized for the smallest tile any split kernel uses (most CTAs, most carry rows)
     int tile = 8 * CSRSPMM_TUNE_TMA_TG;  // TMA kernel
     for (int k = 0; k < kNumShapes; ++k) {
-        const int t = (256 / kShapes[k].G) * kShapes[k].TG;
+        const int t = merge_tile_for(k, (long long)a->M + a->nnz, nullptr);
         if (t < tile) tile = t;
     }
     Plan p;

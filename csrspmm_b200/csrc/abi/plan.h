@@ -18,6 +18,7 @@ struct Plan {
     int shape = 0;                         // index into kShapes (tuning.h)
     bool low_occupancy = false;            // row kernel: fewer than 8 warps of rows per SM
     bool full = false;                     // one pass covers the row exactly: G*NV == ncolv
+    bool small_tile = false;               // merge kernel: CSRSPMM_TUNE_MERGE_TG_SMALL items per lane group
     int G = 8, NV = 1, VW = 4;             // lanes per group, vectors per lane, vector width
     int ncolv = 0;                         // ceil(Nd / VW)
     int tile = 0;                          // merge-path items per CTA (split kernels)
@@ -40,6 +41,10 @@ bool vector_layout_ok(const csrspmm_b200_args* a);
 // Resolves AUTO (and the CSRSPMM_FORCE_KERNEL override) and fills the launch geometry.
 // Returns CSRSPMM_B200_OK or an error status.
 int make_plan(const csrspmm_b200_args* a, Plan* plan);
+
+// Merge-path items per CTA of the merge kernel for lane-group shape `shape` on a problem of
+// `num_items` = M + nnz items (*small says whether the small-problem tile was chosen).
+int merge_tile_for(int shape, long long num_items, bool* small);
 
 // Workspace of the split kernels for a given plan-independent worst case: what
 // csrspmm_b200_workspace_bytes reports (the larger of the MERGE and TMA needs).

@@ -97,7 +97,11 @@
 #endif
 
 // lane-group shapes by dense width class k (column vectors per row <= 8, 16, 32, 64, more):
-// lanes per group G, vectors per lane NV, merge-path items per group TG
+// lanes per group G, vectors per lane NV, merge-path items per group TG.  TG = 192 against 128:
+// fewer, longer-lived CTAs (one search, one staging round and one carry row each) -- config 3
+// 686 -> 654 us, the same matrix at Nd = 128 1361 -> 1285 us, config 5 at a quarter of its rows
+// 10.26 -> 10.04 ms; 224-256 gained nothing more and TG = 256 at G = 16 no longer fits the 48 KB
+// of static shared memory
 #ifndef CSRSPMM_TUNE_S0_G
 #define CSRSPMM_TUNE_S0_G 8
 #endif
@@ -114,7 +118,7 @@
 #define CSRSPMM_TUNE_S1_NV 1
 #endif
 #ifndef CSRSPMM_TUNE_S1_TG
-#define CSRSPMM_TUNE_S1_TG 128
+#define CSRSPMM_TUNE_S1_TG 192
 #endif
 #ifndef CSRSPMM_TUNE_S2_G
 #define CSRSPMM_TUNE_S2_G 32
@@ -123,7 +127,7 @@
 #define CSRSPMM_TUNE_S2_NV 1
 #endif
 #ifndef CSRSPMM_TUNE_S2_TG
-#define CSRSPMM_TUNE_S2_TG 128
+#define CSRSPMM_TUNE_S2_TG 192
 #endif
 #ifndef CSRSPMM_TUNE_S3_G
 #define CSRSPMM_TUNE_S3_G 32
@@ -132,7 +136,7 @@
 #define CSRSPMM_TUNE_S3_NV 2
 #endif
 #ifndef CSRSPMM_TUNE_S3_TG
-#define CSRSPMM_TUNE_S3_TG 128
+#define CSRSPMM_TUNE_S3_TG 192
 #endif
 #ifndef CSRSPMM_TUNE_S4_G
 #define CSRSPMM_TUNE_S4_G 32
@@ -141,10 +145,19 @@
 #define CSRSPMM_TUNE_S4_NV 4
 #endif
 #ifndef CSRSPMM_TUNE_S4_TG
-#define CSRSPMM_TUNE_S4_TG 128
+#define CSRSPMM_TUNE_S4_TG 192
 #endif
 
 namespace csrspmm_b200 {
+
+// merge kernel on small problems: when the regular tiles would give fewer than this many CTAs
+// per SM, lane groups take CSRSPMM_TUNE_MERGE_TG_SMALL items instead, so that the chip still fills
+#ifndef CSRSPMM_TUNE_MERGE_TG_SMALL
+#define CSRSPMM_TUNE_MERGE_TG_SMALL 64
+#endif
+#ifndef CSRSPMM_TUNE_MERGE_SMALL_BELOW_CTAS_PER_SM
+#define CSRSPMM_TUNE_MERGE_SMALL_BELOW_CTAS_PER_SM 2
+#endif
 
 struct ShapeDesc {
     int G, NV, TG;

@@ -155,7 +155,7 @@ int csrspmm_b200_copy_rows(void* dst, size_t dst_pitch_bytes, const void* src, s
  * always runs the merge-path kernel and keeps that kernel's scratch in a fixed array inside the
  * library's device image (CSRSPMM_B200_NOALLOC_SCRATCH_BYTES per GPU, held until the process
  * ends), so it calls no allocation routine at all.  args.kernel / workspace / workspace_bytes are
- * ignored.  A problem whose scratch (an int32 and a row of Nd floats per 1024..2048 of M + nnz)
+ * ignored.  A problem whose scratch (an int32 and a row of Nd floats per 1536..3072 of M + nnz)
  * does not fit is refused with ERR_WORKSPACE and nothing is launched.  Every call on a device
  * shares the one array: the previous call's contents are harmless (every slot that is read is
  * rewritten first by the same call), but two calls running on the GPU at the same time corrupt
