@@ -48,7 +48,7 @@ FALLBACK_HBM_GBS = 6650.0
 # captures summarised under profiles/ (bytes; None = not captured yet)
 NCU_TRAFFIC = {
     # (workload, kernel): (bytes per launch in the capture, non-zeros of the captured case)
-    ("cfg3_powerlaw", "merge"): (3.888e9, 16802627),   # full size, profiles/merge_kernel_cfg3_powerlaw.md
+    ("cfg3_powerlaw", "merge"): (3.641e9, 16802627),   # full size, profiles/merge_kernel_cfg3_powerlaw.md
     ("cfg5_xl", "tma"): (32.88e9, 16777248),           # 1/8 of the rows, profiles/tma_and_merge_kernel_cfg5_xl_eighth.md
     ("cfg5_xl", "merge"): (32.96e9, 16777248),         # 1/8 of the rows, same file
     ("cfg2_medium", "row"): (10.6e6, 268783),          # profiles/row_kernel_cfg2_medium_and_cfg4.md
