@@ -14,6 +14,7 @@ PKG = Path(__file__).resolve().parent
 # CSRSPMM_B200_LIBRARY points at another build of the same library (kernel tuning experiments)
 LIB_PATH = Path(os.environ.get("CSRSPMM_B200_LIBRARY") or PKG / "lib" / "libcsrspmm_b200.so")
 
+ABI_VERSION = 2
 OK = 0
 ERR_BAD_ARG, ERR_INVALID_CSR, ERR_UNSUPPORTED, ERR_CUDA, ERR_DEVICE_WAIT, ERR_WORKSPACE, ERR_NO_DEVICE = range(1, 8)
 
@@ -38,6 +39,7 @@ EXPORTED_SYMBOLS = (
     "csrspmm_b200_dense2csr_fill", "csrspmm_b200_csr2dense", "csrspmm_b200_copy_rows", "csrspmm_b200_column_panels",
     "csrspmm_b200_e2m1_scale_device", "csrspmm_b200_e2m1_encode_device", "csrspmm_b200_e2m1_decode_device",
     "csrspmm_b200_spmm_tiled", "csrspmm_b200_tiled_workspace_bytes", "csrspmm_b200_tiled_panel_rows",
+    "csrspmm_b200_schedule_create", "csrspmm_b200_schedule_destroy", "csrspmm_b200_schedule_info_get",
 )
 
 
@@ -67,7 +69,23 @@ class Args(C.Structure):
         ("workspace", C.c_void_p),
         ("workspace_bytes", C.c_size_t),
         ("status_word", C.c_void_p),
+        ("schedule", C.c_void_p),
     ]
+
+
+class ScheduleOptions(C.Structure):
+    """Mirror of ``csrspmm_b200_schedule_options``."""
+    _fields_ = [("struct_size", C.c_uint32), ("long_row_threshold", C.c_int32), ("slab_rows", C.c_int32),
+                ("piece_nnz", C.c_int32)]
+
+
+class ScheduleInfo(C.Structure):
+    """Mirror of ``csrspmm_b200_schedule_info``."""
+    _fields_ = [("struct_size", C.c_uint32), ("M", C.c_int32), ("Kd", C.c_int32), ("Nd", C.c_int32),
+                ("nnz", C.c_int64), ("long_row_threshold", C.c_int32), ("slab_rows", C.c_int32),
+                ("num_slabs", C.c_int32), ("piece_nnz", C.c_int32), ("long_rows", C.c_int32),
+                ("long_nnz", C.c_int64), ("pieces", C.c_int64), ("columns_sorted", C.c_int32),
+                ("device_bytes", C.c_size_t), ("build_ms", C.c_double)]
 
 
 class LibraryMissing(RuntimeError):
@@ -153,8 +171,15 @@ def lib() -> C.CDLL:
     L.csrspmm_b200_csr2dense.argtypes = [C.c_int32, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64,
                                          C.c_void_p]
     L.csrspmm_b200_csr2dense.restype = C.c_int
-    if L.csrspmm_b200_abi_version() != 1:
-        raise LibraryMissing(f"{LIB_PATH} has ABI version {L.csrspmm_b200_abi_version()}, expected 1")
+    L.csrspmm_b200_schedule_create.argtypes = [C.POINTER(Args), C.POINTER(ScheduleOptions), C.POINTER(C.c_void_p),
+                                               C.c_void_p]
+    L.csrspmm_b200_schedule_create.restype = C.c_int
+    L.csrspmm_b200_schedule_destroy.argtypes = [C.c_void_p]
+    L.csrspmm_b200_schedule_destroy.restype = C.c_int
+    L.csrspmm_b200_schedule_info_get.argtypes = [C.c_void_p, C.POINTER(ScheduleInfo)]
+    L.csrspmm_b200_schedule_info_get.restype = C.c_int
+    if L.csrspmm_b200_abi_version() != ABI_VERSION:
+        raise LibraryMissing(f"{LIB_PATH} has ABI version {L.csrspmm_b200_abi_version()}, expected {ABI_VERSION}")
     _lib = L
     return L
 
@@ -162,7 +187,7 @@ def lib() -> C.CDLL:
 def make_args(M, Kd, Nd, nnz, row_ptr=0, col_idx=0, values=0, B=0, Cptr=0, *, ldb=None, ldc=None,
               alpha=1.0, beta=0.0, entry=ENTRY_NAIVE, kernel=KERNEL_AUTO, max_row_nnz=0,
               value_format=VALUES_F32, value_scale=1.0, workspace=0, workspace_bytes=0,
-              status_word=0, row_ptr_base=0) -> Args:
+              status_word=0, row_ptr_base=0, schedule=0) -> Args:
     a = Args()
     a.struct_size = C.sizeof(Args)
     a.M, a.Kd, a.Nd, a.nnz = int(M), int(Kd), int(Nd), int(nnz)
@@ -175,6 +200,7 @@ def make_args(M, Kd, Nd, nnz, row_ptr=0, col_idx=0, values=0, B=0, Cptr=0, *, ld
     a.row_ptr_base = int(row_ptr_base)
     a.workspace, a.workspace_bytes = workspace or None, int(workspace_bytes)
     a.status_word = status_word or None
+    a.schedule = schedule or None
     return a
 
 

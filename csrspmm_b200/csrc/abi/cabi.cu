@@ -15,9 +15,47 @@
 #include "../kernels/row_kernel.cuh"
 #include "../kernels/tma_kernel.cuh"
 #include "csrspmm_b200.h"
+#include "launch.h"
 #include "plan.h"
 
 using namespace csrspmm_b200;
+
+namespace csrspmm_b200 {
+
+void fill_params(const csrspmm_b200_args* a, const Plan& plan, SpmmParams* out)
+{
+    SpmmParams p;
+    std::memset(&p, 0, sizeof(p));
+    p.M = a->M;
+    p.Kd = a->Kd;
+    p.Nd = a->Nd;
+    p.nnz = (int)a->nnz;
+    p.ncolv = plan.ncolv;
+    p.num_items = plan.num_items;
+    p.row_ptr = a->row_ptr;
+    p.rp_base = a->row_ptr_base;
+    p.col_idx = a->col_idx;
+    p.values = a->values;
+    p.value_scale = a->value_scale;
+    p.B = a->B;
+    p.ldb = a->ldb;
+    p.ldb_bytes = (unsigned)(a->ldb * 4);
+    p.C = a->C;
+    p.ldc = a->ldc;
+    p.alpha = a->alpha;
+    p.beta = a->beta;
+    p.status_word = a->status_word;
+    *out = p;
+}
+
+void set_carry_scratch(const Plan& plan, void* workspace, SpmmParams* p)
+{
+    p->carry_row = static_cast<int*>(workspace);
+    p->carry_val = reinterpret_cast<float*>(static_cast<char*>(workspace) + plan.carry_row_bytes);
+    p->carry_ld = plan.carry_ld;
+}
+
+}  // namespace csrspmm_b200
 
 namespace {
 
@@ -49,22 +87,6 @@ void launch_row(const SpmmParams& p, const Plan& plan, cudaStream_t st)
             spmm_row_kernel<G, NV, VW, ULOW, FMT, false, 2><<<grid, kRowThreads, 0, st>>>(p);
         else
             spmm_row_kernel<G, NV, VW, U, FMT, false, MINB><<<grid, kRowThreads, 0, st>>>(p);
-    }
-}
-
-template <int S, int VW, int FMT>
-void launch_merge(const SpmmParams& p, const Plan& plan, cudaStream_t st)
-{
-    constexpr int G = kShapes[S].G, NV = kShapes[S].NV, TG = kShapes[S].TG;
-    constexpr int TGS = CSRSPMM_TUNE_MERGE_TG_SMALL < TG ? CSRSPMM_TUNE_MERGE_TG_SMALL : TG;
-    constexpr int U = VW == 1 ? 8 : merge_unroll(NV);
-    const unsigned grid = (unsigned)plan.grid;
-    if (plan.small_tile) {  // few items: smaller tiles, more CTAs
-        if (VW == 4 && plan.full) spmm_merge_kernel<G, NV, VW, TGS, U, FMT, (VW == 4)><<<grid, kMergeThreads, 0, st>>>(p);
-        else spmm_merge_kernel<G, NV, VW, TGS, U, FMT, false><<<grid, kMergeThreads, 0, st>>>(p);
-    } else {
-        if (VW == 4 && plan.full) spmm_merge_kernel<G, NV, VW, TG, U, FMT, (VW == 4)><<<grid, kMergeThreads, 0, st>>>(p);
-        else spmm_merge_kernel<G, NV, VW, TG, U, FMT, false><<<grid, kMergeThreads, 0, st>>>(p);
     }
 }
 
@@ -104,18 +126,6 @@ void dispatch_row(const SpmmParams& p, const Plan& plan, cudaStream_t st)
     }
 }
 
-template <int VW, int FMT>
-void dispatch_merge(const SpmmParams& p, const Plan& plan, cudaStream_t st)
-{
-    switch (plan.shape) {
-        case 0: launch_merge<0, VW, FMT>(p, plan, st); break;
-        case 1: launch_merge<1, VW, FMT>(p, plan, st); break;
-        case 2: launch_merge<2, VW, FMT>(p, plan, st); break;
-        case 3: launch_merge<3, VW, FMT>(p, plan, st); break;
-        default: launch_merge<4, VW, FMT>(p, plan, st); break;
-    }
-}
-
 template <int FMT>
 cudaError_t dispatch_tma(const SpmmParams& p, const Plan& plan, cudaStream_t st)
 {
@@ -149,31 +159,14 @@ int enqueue(const csrspmm_b200_args* a, cudaStream_t st)
         if (status != CSRSPMM_B200_OK) return status;
     }
 
+    if (schedule_applies(a)) return enqueue_scheduled(a, st);
+
     Plan plan;
     status = make_plan(a, &plan);
     if (status != CSRSPMM_B200_OK) return status;
 
     SpmmParams p;
-    std::memset(&p, 0, sizeof(p));
-    p.M = a->M;
-    p.Kd = a->Kd;
-    p.Nd = a->Nd;
-    p.nnz = (int)a->nnz;
-    p.ncolv = plan.ncolv;
-    p.num_items = plan.num_items;
-    p.row_ptr = a->row_ptr;
-    p.rp_base = a->row_ptr_base;
-    p.col_idx = a->col_idx;
-    p.values = a->values;
-    p.value_scale = a->value_scale;
-    p.B = a->B;
-    p.ldb = a->ldb;
-    p.ldb_bytes = (unsigned)(a->ldb * 4);
-    p.C = a->C;
-    p.ldc = a->ldc;
-    p.alpha = a->alpha;
-    p.beta = a->beta;
-    p.status_word = a->status_word;
+    fill_params(a, plan, &p);
 
     const bool split = plan.kernel != CSRSPMM_B200_KERNEL_ROW;
     void* ws = nullptr;
@@ -191,41 +184,21 @@ int enqueue(const csrspmm_b200_args* a, cudaStream_t st)
             CUDA_TRY(cudaMallocAsync(&ws, plan.workspace_bytes, st));
             ws_owned = true;
         }
-        p.carry_row = static_cast<int*>(ws);
-        p.carry_val = reinterpret_cast<float*>(static_cast<char*>(ws) + plan.carry_row_bytes);
-        p.carry_ld = plan.carry_ld;
+        set_carry_scratch(plan, ws, &p);
     }
 
     const bool e2m1 = a->value_format == CSRSPMM_B200_VALUES_E2M1;
     cudaError_t attr_err = cudaSuccess;
     if (plan.kernel == CSRSPMM_B200_KERNEL_ROW) {
-        if (plan.VW == 4) {
-            if (e2m1) dispatch_row<4, kValuesE2M1>(p, plan, st);
-            else dispatch_row<4, kValuesF32>(p, plan, st);
-        } else {
-            if (e2m1) dispatch_row<1, kValuesE2M1>(p, plan, st);
-            else dispatch_row<1, kValuesF32>(p, plan, st);
-        }
+        attr_err = launch_row_kernel(p, plan, e2m1, st);
     } else if (plan.kernel == CSRSPMM_B200_KERNEL_MERGE) {
-        if (plan.VW == 4) {
-            if (e2m1) dispatch_merge<4, kValuesE2M1>(p, plan, st);
-            else dispatch_merge<4, kValuesF32>(p, plan, st);
-        } else {
-            if (e2m1) dispatch_merge<1, kValuesE2M1>(p, plan, st);
-            else dispatch_merge<1, kValuesF32>(p, plan, st);
-        }
+        attr_err = launch_merge_kernel(p, plan, e2m1, st);
     } else {
         attr_err = e2m1 ? dispatch_tma<kValuesE2M1>(p, plan, st) : dispatch_tma<kValuesF32>(p, plan, st);
     }
     cudaError_t err = attr_err != cudaSuccess ? attr_err : cudaGetLastError();
 
-    if (err == cudaSuccess && split) {
-        const int warps = 256 / 32;
-        const unsigned grid = (unsigned)((plan.num_tiles + warps - 1) / warps);
-        if (plan.VW == 4) spmm_fixup_kernel<4><<<grid, 256, 0, st>>>(p, (int)plan.num_tiles);
-        else spmm_fixup_kernel<1><<<grid, 256, 0, st>>>(p, (int)plan.num_tiles);
-        err = cudaGetLastError();
-    }
+    if (err == cudaSuccess && split) err = launch_fixup_kernel(p, plan, st);
     if (ws_owned) {
         cudaError_t ferr = cudaFreeAsync(ws, st);
         if (err == cudaSuccess) err = ferr;
@@ -364,6 +337,22 @@ int spmm_host_panels(const csrspmm_b200_args* a, const HostBuffers& d, int panel
 
 }  // namespace
 
+namespace csrspmm_b200 {
+
+cudaError_t launch_row_kernel(const SpmmParams& p, const Plan& plan, bool e2m1, cudaStream_t st)
+{
+    if (plan.VW == 4) {
+        if (e2m1) dispatch_row<4, kValuesE2M1>(p, plan, st);
+        else dispatch_row<4, kValuesF32>(p, plan, st);
+    } else {
+        if (e2m1) dispatch_row<1, kValuesE2M1>(p, plan, st);
+        else dispatch_row<1, kValuesF32>(p, plan, st);
+    }
+    return cudaGetLastError();
+}
+
+}  // namespace csrspmm_b200
+
 extern "C" {
 
 int csrspmm_b200_abi_version(void) { return CSRSPMM_B200_ABI_VERSION; }
@@ -411,7 +400,12 @@ int csrspmm_b200_spmm_sync(const csrspmm_b200_args* args, csrspmm_b200_stream_t 
     return CSRSPMM_B200_OK;
 }
 
-size_t csrspmm_b200_workspace_bytes(const csrspmm_b200_args* args) { return worst_case_workspace(args); }
+size_t csrspmm_b200_workspace_bytes(const csrspmm_b200_args* args)
+{
+    if (args != nullptr && args->struct_size == sizeof(csrspmm_b200_args) && schedule_applies(args))
+        return scheduled_workspace_bytes(args);
+    return worst_case_workspace(args);
+}
 
 int csrspmm_b200_select_kernel(const csrspmm_b200_args* args)
 {
@@ -432,7 +426,7 @@ size_t csrspmm_b200_host_arena_bytes(const csrspmm_b200_args* a)
     total += align256(vbytes);
     total += align256((size_t)a->Kd * (size_t)a->Nd * 4);
     total += align256((size_t)a->M * (size_t)a->Nd * 4);
-    total += align256(worst_case_workspace(a));
+    total += align256(worst_case_workspace(a, true));  // row blocks share it
     total += 256;  // status word
     return total;
 }
@@ -464,7 +458,7 @@ int csrspmm_b200_spmm_host(const csrspmm_b200_args* a, void* device_arena, size_
     const size_t vbytes = e2m1 ? (size_t)(a->nnz + 1) / 2 : (size_t)a->nnz * 4;
     const size_t rp_bytes = ((size_t)a->M + 1) * 4, ci_bytes = (size_t)a->nnz * 4;
     const size_t c_bytes = (size_t)a->M * (size_t)a->Nd * 4;
-    const size_t ws_bytes = worst_case_workspace(a);
+    const size_t ws_bytes = worst_case_workspace(a, true);  // enough for every row block below
     char* cur = arena;
     int32_t* d_rp = reinterpret_cast<int32_t*>(cur); cur += align256(rp_bytes);
     int32_t* d_ci = reinterpret_cast<int32_t*>(cur); cur += align256(ci_bytes);

@@ -13,7 +13,7 @@
 // Limits and rules.
 //   * The array is CSRSPMM_B200_NOALLOC_SCRATCH_BYTES (8 MiB) per device and exists on every GPU
 //     that loads the library, until the process ends.  A problem that needs more (one int32 plus
-//     one row of Nd floats per 1536 to 3072 merge-path items) is refused with ERR_WORKSPACE and a
+//     one row of Nd floats per CTA of the merge kernel, i.e. per 512 to 3072 merge-path items) is refused with ERR_WORKSPACE and a
 //     message that states both numbers; nothing is launched.
 //   * It always runs the merge-path kernel (args.kernel, args.workspace, args.workspace_bytes
 //     are ignored).
@@ -31,8 +31,8 @@
 #include <cstring>
 #include <mutex>
 
-#include "../kernels/merge_kernel.cuh"
 #include "csrspmm_b200.h"
+#include "launch.h"
 #include "plan.h"
 
 using namespace csrspmm_b200;
@@ -74,28 +74,6 @@ int scratch_of_current_device(void** out)
     return CSRSPMM_B200_OK;
 }
 
-template <int S, int VW, int FMT>
-void launch_one(const SpmmParams& p, const Plan& plan, cudaStream_t st)
-{
-    constexpr int G = kShapes[S].G, NV = kShapes[S].NV, TG = kShapes[S].TG;
-    constexpr int TGS = CSRSPMM_TUNE_MERGE_TG_SMALL < TG ? CSRSPMM_TUNE_MERGE_TG_SMALL : TG;
-    constexpr int U = VW == 1 ? 8 : merge_unroll(NV);
-    if (plan.small_tile) spmm_merge_kernel<G, NV, VW, TGS, U, FMT, false><<<(unsigned)plan.grid, kMergeThreads, 0, st>>>(p);
-    else spmm_merge_kernel<G, NV, VW, TG, U, FMT, false><<<(unsigned)plan.grid, kMergeThreads, 0, st>>>(p);
-}
-
-template <int VW, int FMT>
-void launch_merge_for_shape(const SpmmParams& p, const Plan& plan, cudaStream_t st)
-{
-    switch (plan.shape) {
-        case 0: launch_one<0, VW, FMT>(p, plan, st); break;
-        case 1: launch_one<1, VW, FMT>(p, plan, st); break;
-        case 2: launch_one<2, VW, FMT>(p, plan, st); break;
-        case 3: launch_one<3, VW, FMT>(p, plan, st); break;
-        default: launch_one<4, VW, FMT>(p, plan, st); break;
-    }
-}
-
 }  // namespace
 
 extern "C" int csrspmm_b200_spmm_noalloc(const csrspmm_b200_args* args, csrspmm_b200_stream_t stream)
@@ -108,6 +86,7 @@ extern "C" int csrspmm_b200_spmm_noalloc(const csrspmm_b200_args* args, csrspmm_
     a.kernel = CSRSPMM_B200_KERNEL_MERGE;
     a.workspace = nullptr;
     a.workspace_bytes = 0;
+    a.schedule = nullptr;  // a schedule's scratch would not fit the fixed array's contract
     Plan plan;
     status = make_plan(&a, &plan);
     if (status != CSRSPMM_B200_OK) return status;
@@ -121,47 +100,14 @@ extern "C" int csrspmm_b200_spmm_noalloc(const csrspmm_b200_args* args, csrspmm_
     status = scratch_of_current_device(&scratch);
     if (status != CSRSPMM_B200_OK) return status;
 
+    // same parameter block, same kernel dispatch and same fix-up as csrspmm_b200_spmm's merge path
     SpmmParams p;
-    std::memset(&p, 0, sizeof(p));
-    p.M = a.M;
-    p.Kd = a.Kd;
-    p.Nd = a.Nd;
-    p.nnz = (int)a.nnz;
-    p.ncolv = plan.ncolv;
-    p.num_items = plan.num_items;
-    p.row_ptr = a.row_ptr;
-    p.rp_base = a.row_ptr_base;
-    p.col_idx = a.col_idx;
-    p.values = a.values;
-    p.value_scale = a.value_scale;
-    p.B = a.B;
-    p.ldb = a.ldb;
-    p.ldb_bytes = (unsigned)(a.ldb * 4);
-    p.C = a.C;
-    p.ldc = a.ldc;
-    p.alpha = a.alpha;
-    p.beta = a.beta;
-    p.status_word = a.status_word;
-    p.carry_row = static_cast<int*>(scratch);
-    p.carry_val = reinterpret_cast<float*>(static_cast<char*>(scratch) + plan.carry_row_bytes);
-    p.carry_ld = plan.carry_ld;
+    fill_params(&a, plan, &p);
+    set_carry_scratch(plan, scratch, &p);
 
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-    const bool e2m1 = a.value_format == CSRSPMM_B200_VALUES_E2M1;
-    if (plan.VW == 4) {
-        if (e2m1) launch_merge_for_shape<4, kValuesE2M1>(p, plan, st);
-        else launch_merge_for_shape<4, kValuesF32>(p, plan, st);
-    } else {
-        if (e2m1) launch_merge_for_shape<1, kValuesE2M1>(p, plan, st);
-        else launch_merge_for_shape<1, kValuesF32>(p, plan, st);
-    }
-    cudaError_t err = cudaGetLastError();
-    if (err == cudaSuccess) {
-        const unsigned grid = (unsigned)((plan.num_tiles + 7) / 8);
-        if (plan.VW == 4) spmm_fixup_kernel<4><<<grid, 256, 0, st>>>(p, (int)plan.num_tiles);
-        else spmm_fixup_kernel<1><<<grid, 256, 0, st>>>(p, (int)plan.num_tiles);
-        err = cudaGetLastError();
-    }
+    cudaError_t err = launch_merge_kernel(p, plan, a.value_format == CSRSPMM_B200_VALUES_E2M1, st);
+    if (err == cudaSuccess) err = launch_fixup_kernel(p, plan, st);
     if (err != cudaSuccess) {
         set_last_error("csrspmm_b200_spmm_noalloc: kernel launch failed: %s", cudaGetErrorString(err));
         return CSRSPMM_B200_ERR_CUDA;

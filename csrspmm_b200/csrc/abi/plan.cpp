@@ -218,13 +218,16 @@ int make_plan(const csrspmm_b200_args* a, Plan* plan)
     return CSRSPMM_B200_OK;
 }
 
-size_t worst_case_workspace(const csrspmm_b200_args* a)
+size_t worst_case_workspace(const csrspmm_b200_args* a, bool any_row_block)
 {
     if (check_args(a, false) != CSRSPMM_B200_OK) return 0;
-    // sized for the smallest tile any split kernel uses (most CTAs, most carry rows)
+    // sized for the smallest tile any split kernel uses (most CTAs, most carry rows).  A row block of
+    // a large matrix may fall under the small-problem threshold although the whole matrix does not,
+    // so a caller that multiplies row blocks out of one scratch buffer asks for the small tile
+    // whatever the size (any_row_block).
     int tile = 8 * CSRSPMM_TUNE_TMA_TG;  // TMA kernel
     for (int k = 0; k < kNumShapes; ++k) {
-        const int t = merge_tile_for(k, (long long)a->M + a->nnz, nullptr);
+        const int t = merge_tile_for(k, any_row_block ? 0 : (long long)a->M + a->nnz, nullptr);
         if (t < tile) tile = t;
     }
     Plan p;

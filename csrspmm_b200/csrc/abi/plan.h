@@ -18,7 +18,7 @@ struct Plan {
     int shape = 0;                         // index into kShapes (tuning.h)
     bool low_occupancy = false;            // row kernel: fewer than 8 warps of rows per SM
     bool full = false;                     // one pass covers the row exactly: G*NV == ncolv
-    bool small_tile = false;               // merge kernel: CSRSPMM_TUNE_MERGE_TG_SMALL items per lane group
+    bool small_tile = false;               // merge kernel: the small-problem tile (fewer items per lane group)
     int G = 8, NV = 1, VW = 4;             // lanes per group, vectors per lane, vector width
     int ncolv = 0;                         // ceil(Nd / VW)
     int tile = 0;                          // merge-path items per CTA (split kernels)
@@ -47,8 +47,9 @@ int make_plan(const csrspmm_b200_args* a, Plan* plan);
 int merge_tile_for(int shape, long long num_items, bool* small);
 
 // Workspace of the split kernels for a given plan-independent worst case: what
-// csrspmm_b200_workspace_bytes reports (the larger of the MERGE and TMA needs).
-size_t worst_case_workspace(const csrspmm_b200_args* a);
+// csrspmm_b200_workspace_bytes reports (the larger of the MERGE and TMA needs).  any_row_block:
+// also enough for any contiguous block of the matrix's rows multiplied on its own.
+size_t worst_case_workspace(const csrspmm_b200_args* a, bool any_row_block = false);
 
 void set_last_error(const char* fmt, ...);
 const char* get_last_error();

@@ -45,6 +45,8 @@ struct SpmmParams {
     float* carry_val;    // one row of carry_ld floats per tile
     long long carry_ld;  // multiple of 4
     int* status_word;    // may be null
+    int skip_len;        // merge kernel with SKIP: rows of this many entries or more are left to the
+                         // scheduled pieces (neither summed nor written); 0 = every row is mine
 };
 
 __device__ __forceinline__ void report_status(const SpmmParams& p, int bit)
@@ -94,6 +96,27 @@ __device__ __forceinline__ unsigned long long make_b_policy()
     return pol;
 }
 
+// ---- asynchronous global -> shared copies (per-thread completion groups) ----------------------------
+__device__ __forceinline__ unsigned smem_addr(const void* p) { return static_cast<unsigned>(__cvta_generic_to_shared(p)); }
+
+template <int VW>
+__device__ __forceinline__ void async_copy_vec(unsigned dst, const void* src)
+{
+    if constexpr (VW == 4) asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+    else asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
+}
+template <int VW>
+__device__ __forceinline__ void async_copy_vec_hint(unsigned dst, const void* src, unsigned long long policy)
+{
+    if constexpr (VW == 4)
+        asm volatile("cp.async.cg.shared.global.L2::cache_hint [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "l"(policy) : "memory");
+    else
+        asm volatile("cp.async.ca.shared.global.L2::cache_hint [%0], [%1], 4, %2;" ::"r"(dst), "l"(src), "l"(policy) : "memory");
+}
+__device__ __forceinline__ void async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
 // ---- column vectors (VW = 4: float4, 16-byte aligned; VW = 1: one float) --------------------------
 
 template <int VW>
@@ -114,6 +137,13 @@ struct Vec<4> {
         (void)pol;
         load_nc(p);
 #endif
+    }
+    // read-only load carrying an L2 eviction policy made by createpolicy
+    __device__ __forceinline__ void load_hint(const float* p, unsigned long long pol)
+    {
+        asm("ld.global.nc.L2::cache_hint.v4.f32 {%0, %1, %2, %3}, [%4], %5;"
+            : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+            : "l"(p), "l"(pol));
     }
     __device__ __forceinline__ void load(const float* p) { v = *reinterpret_cast<const float4*>(p); }
     __device__ __forceinline__ void store(float* p) const { *reinterpret_cast<float4*>(p) = v; }
@@ -176,6 +206,10 @@ struct Vec<1> {
         (void)pol;
         load_nc(p);
 #endif
+    }
+    __device__ __forceinline__ void load_hint(const float* p, unsigned long long pol)
+    {
+        asm("ld.global.nc.L2::cache_hint.f32 %0, [%1], %2;" : "=f"(v) : "l"(p), "l"(pol));
     }
     __device__ __forceinline__ void load(const float* p) { v = *p; }
     __device__ __forceinline__ void store(float* p) const { *p = v; }

@@ -82,8 +82,10 @@ struct MergeSmem {
     alignas(8) int2 cv[TILE];  // (column index, value bits) of each staged non-zero
     int coord[4];
     int tail_row[GROUPS];
+    unsigned longbits[TILE / 32 + 1];  // SKIP only: bit k = local row k is left to the scheduled pieces
     alignas(16) float tail[GROUPS][ROWW];
     __device__ __forceinline__ float* tail_of(int g) { return tail[g]; }
+    __device__ __forceinline__ bool is_long(int k) const { return (longbits[k >> 5] >> (k & 31)) & 1u; }
 };
 
 // Where a lane group's share of the tile starts and ends, in tile-local coordinates.
@@ -96,7 +98,9 @@ struct TileRange {
 };
 
 // Steps 1-3.  Returns false (for every thread of the CTA) when row_ptr is inconsistent.
-template <class Smem, int G, int TG, int FMT>
+// SKIP: rows of p.skip_len entries or more belong to the scheduled pieces; they are marked in
+// s.longbits and 32-entry runs that lie wholly inside such a row are not fetched.
+template <class Smem, int G, int TG, int FMT, bool SKIP = false>
 __device__ __forceinline__ bool merge_tile_setup(const SpmmParams& p, Smem& s, TileRange& r)
 {
     constexpr int TILE = Smem::TILE;
@@ -129,9 +133,42 @@ __device__ __forceinline__ bool merge_tile_setup(const SpmmParams& p, Smem& s, T
     }
 
     // ---- 2. stage the slice ----------------------------------------------------------------
-    for (int k = tid; k <= r.nrows; k += kMergeThreads)
-        s.rowend[k] = (k < r.nrows) ? (__ldg(row_end + r.i0 + k) - p.rp_base - r.j0) : INT_MAX;
+    if constexpr (SKIP) {
+        for (int k0 = warp * 32; k0 <= r.nrows; k0 += kMergeThreads) {  // whole warps: one flag word each
+            const int k = k0 + (tid & 31);
+            bool is_long = false;
+            if (k <= r.nrows) {
+                const long long gi = (long long)r.i0 + k;
+                int end = 0;
+                if (gi < p.M) {
+                    end = __ldg(row_end + gi);
+                    is_long = end - __ldg(p.row_ptr + gi) >= p.skip_len;
+                }
+                s.rowend[k] = (k < r.nrows) ? (end - p.rp_base - r.j0) : INT_MAX;
+            }
+            const unsigned bits = __ballot_sync(0xffffffffu, is_long);
+            if ((tid & 31) == 0) s.longbits[k0 >> 5] = bits;
+        }
+        __syncthreads();
+    } else {
+        for (int k = tid; k <= r.nrows; k += kMergeThreads)
+            s.rowend[k] = (k < r.nrows) ? (__ldg(row_end + r.i0 + k) - p.rp_base - r.j0) : INT_MAX;
+    }
     for (int k = tid; k < r.nnzt; k += kMergeThreads) {
+        if constexpr (SKIP) {
+            // the row that holds the first entry of this warp's run of 32
+            const int k0 = k & ~31;
+            int lo = 0, hi = r.nrows;
+            while (lo < hi) {
+                const int mid = (lo + hi) >> 1;
+                if (s.rowend[mid] <= k0) lo = mid + 1;
+                else hi = mid;
+            }
+            if (s.is_long(lo) && s.rowend[lo] >= min(k0 + 32, r.nnzt)) {
+                s.cv[k] = make_int2(0, 0);  // never read as data, but a batch may gather row 0 of B for it
+                continue;
+            }
+        }
         int c = __ldcs(p.col_idx + r.j0 + k);
         if ((unsigned)c >= (unsigned)p.Kd) {  // never fault on a bad index
             c = min(max(c, 0), p.Kd - 1);
@@ -155,10 +192,11 @@ __device__ __forceinline__ bool merge_tile_setup(const SpmmParams& p, Smem& s, T
 
 // Steps 4-5 for one column pass.  acc = the group's unfinished partial sum (valid when dirty),
 // head = its held-back first finished row (valid when il1 > il0).  Contains one __syncthreads.
+// head_skip: the group's first finished row belongs to the scheduled pieces and is not written.
 template <class Smem, int G, int NV, int VW>
 __device__ __forceinline__ void merge_tile_finish(const SpmmParams& p, Smem& s, const TileRange& r,
                                                   int cb, int g, int lane, const Vec<VW> (&acc)[NV],
-                                                  Vec<VW> (&head)[NV], bool dirty)
+                                                  Vec<VW> (&head)[NV], bool dirty, bool head_skip = false)
 {
     constexpr int GROUPS = Smem::GROUPS;
     // ---- 4. rows shared between groups of this CTA -------------------------------------------
@@ -169,7 +207,7 @@ __device__ __forceinline__ void merge_tile_finish(const SpmmParams& p, Smem& s, 
     }
     __syncthreads();
 
-    if (r.il1 > r.il0) {
+    if (r.il1 > r.il0 && !head_skip) {
         // earlier groups' partial sums of my first row, oldest first, then my own part
         int gs = g;
         while (gs > 0 && s.tail_row[gs - 1] == r.il0) --gs;
@@ -220,14 +258,18 @@ __device__ __forceinline__ void merge_tile_finish(const SpmmParams& p, Smem& s, 
 }
 
 // FULL: one pass covers the row exactly (G * NV == ncolv), so no column guard is compiled in.
-template <int G, int NV, int VW, int TG, int U, int FMT, bool FULL>
+// SKIP: the product runs under a schedule; rows of p.skip_len entries or more are summed by the
+// scheduled pieces (sliced_kernel.cuh) and this kernel neither reads their entries nor writes
+// their rows of C.  The tiles still count those rows' items, so a tile inside a hub row is a
+// search and an exit.
+template <int G, int NV, int VW, int TG, int U, int FMT, bool FULL, bool SKIP = false>
 __global__ void __launch_bounds__(kMergeThreads, merge_min_blocks(NV)) spmm_merge_kernel(const SpmmParams p)
 {
     using Smem = MergeSmem<G, NV, VW, TG>;
     __shared__ Smem s;
 
     TileRange r;
-    if (!merge_tile_setup<Smem, G, TG, FMT>(p, s, r)) return;
+    if (!merge_tile_setup<Smem, G, TG, FMT, SKIP>(p, s, r)) return;
     const int g = threadIdx.x / G;
     const int lane = threadIdx.x % G;
     const char* const b_lane = reinterpret_cast<const char*>(p.B) + (size_t)lane * (VW * 4);
@@ -249,9 +291,14 @@ __global__ void __launch_bounds__(kMergeThreads, merge_min_blocks(NV)) spmm_merg
         int i = r.il0;
         int next_end = s.rowend[i];  // local position where row i ends (INT_MAX past the tile's rows)
         bool dirty = false;
+        bool skip = false;       // SKIP: row i belongs to the scheduled pieces
+        bool head_skip = false;  // SKIP: so did the first row this group finished
+        if constexpr (SKIP) skip = s.is_long(i);
 
         auto finish_row = [&]() {
-            if (i == r.il0) {
+            if (SKIP && skip) {
+                if (i == r.il0) head_skip = true;
+            } else if (i == r.il0) {
 #pragma unroll
                 for (int v = 0; v < NV; ++v) head[v] = acc[v];
             } else {
@@ -262,6 +309,7 @@ __global__ void __launch_bounds__(kMergeThreads, merge_min_blocks(NV)) spmm_merg
             dirty = false;
             ++i;
             next_end = s.rowend[i];
+            if constexpr (SKIP) skip = s.is_long(i);
         };
 
         // B row of staged non-zero e: one 32x32->64 multiply-add gives the address
@@ -275,6 +323,55 @@ __global__ void __launch_bounds__(kMergeThreads, merge_min_blocks(NV)) spmm_merg
         };
 
         int base = r.jl0;
+        if constexpr (SKIP) {
+            // as below, but a scheduled row is jumped over: to its end when that lies in this
+            // group's range (rows before il1 end at or before jl1), else to the end of the range
+            while (base < r.jl1) {
+                while (base >= next_end) finish_row();  // an entry exists at `base`, so these ends are mine
+                if (skip) {
+                    if (i < r.il1) {
+                        base = next_end;
+                        finish_row();
+                    } else {
+                        base = r.jl1;
+                    }
+                    continue;
+                }
+                const int n = min(U, r.jl1 - base);
+                int2 e[U];
+                Vec<VW> bq[U][NV];
+#pragma unroll
+                for (int u = 0; u < U; ++u) {
+                    if (u < n) {
+                        e[u] = s.cv[base + u];
+                        load_b(bq[u], e[u].x);
+                    }
+                }
+                if (n == U && base + U <= next_end) {
+#pragma unroll
+                    for (int u = 0; u < U; ++u) {
+                        const float a = __int_as_float(e[u].y);
+#pragma unroll
+                        for (int v = 0; v < NV; ++v) acc[v].fma(a, bq[u][v]);
+                    }
+                    dirty = true;
+                } else {
+#pragma unroll
+                    for (int u = 0; u < U; ++u) {
+                        if (u < n) {
+                            while (base + u >= next_end) finish_row();
+                            if (!skip) {
+                                const float a = __int_as_float(e[u].y);
+#pragma unroll
+                                for (int v = 0; v < NV; ++v) acc[v].fma(a, bq[u][v]);
+                                dirty = true;
+                            }
+                        }
+                    }
+                }
+                base += n;
+            }
+        } else {
         // whole batches of U non-zeros: loads first (they do not depend on the row structure),
         // then the multiply-adds, without any per-element test when no row ends inside the batch
         for (; base + U <= r.jl1; base += U) {
@@ -326,9 +423,10 @@ __global__ void __launch_bounds__(kMergeThreads, merge_min_blocks(NV)) spmm_merg
                 }
             }
         }
+        }  // !SKIP
         while (i < r.il1) finish_row();
 
-        merge_tile_finish<Smem, G, NV, VW>(p, s, r, cb, g, lane, acc, head, dirty);
+        merge_tile_finish<Smem, G, NV, VW>(p, s, r, cb, g, lane, acc, head, dirty, head_skip);
         if (cb + G * NV < p.ncolv) __syncthreads();  // tails are rewritten by the next pass
     }
 }

@@ -24,6 +24,65 @@
 #define CSRSPMM_TUNE_ROW_U_NV4 4
 #endif
 
+// scheduled pieces (sliced_kernel.cuh): consecutive pieces per lane group
+#ifndef CSRSPMM_TUNE_SLICED_PIECES_PER_GROUP
+#define CSRSPMM_TUNE_SLICED_PIECES_PER_GROUP 2
+#endif
+// scheduled pieces load B with an evict_last policy (1) or plainly (0)
+#ifndef CSRSPMM_TUNE_SLICED_EVICT_LAST
+#define CSRSPMM_TUNE_SLICED_EVICT_LAST 0
+#endif
+
+// Scheduled pieces (sliced_kernel.cuh): the gather is pipelined through shared memory, no gathered
+// row is held in registers, so a lane can own more column vectors and a warp more pieces.  Per dense
+// width class k: lanes per group G, vectors per lane NV, rows of B in flight per group D (a multiple
+// of 4 and a power of two; G*NV*16*D*(256/G) = 64 KB of ring per CTA at every width).
+#ifndef CSRSPMM_TUNE_P0_G
+#define CSRSPMM_TUNE_P0_G 8
+#endif
+#ifndef CSRSPMM_TUNE_P0_NV
+#define CSRSPMM_TUNE_P0_NV 1
+#endif
+#ifndef CSRSPMM_TUNE_P0_D
+#define CSRSPMM_TUNE_P0_D 16
+#endif
+#ifndef CSRSPMM_TUNE_P1_G
+#define CSRSPMM_TUNE_P1_G 8
+#endif
+#ifndef CSRSPMM_TUNE_P1_NV
+#define CSRSPMM_TUNE_P1_NV 2
+#endif
+#ifndef CSRSPMM_TUNE_P1_D
+#define CSRSPMM_TUNE_P1_D 8
+#endif
+#ifndef CSRSPMM_TUNE_P2_G
+#define CSRSPMM_TUNE_P2_G 16
+#endif
+#ifndef CSRSPMM_TUNE_P2_NV
+#define CSRSPMM_TUNE_P2_NV 2
+#endif
+#ifndef CSRSPMM_TUNE_P2_D
+#define CSRSPMM_TUNE_P2_D 8
+#endif
+#ifndef CSRSPMM_TUNE_P3_G
+#define CSRSPMM_TUNE_P3_G 32
+#endif
+#ifndef CSRSPMM_TUNE_P3_NV
+#define CSRSPMM_TUNE_P3_NV 2
+#endif
+#ifndef CSRSPMM_TUNE_P3_D
+#define CSRSPMM_TUNE_P3_D 8
+#endif
+#ifndef CSRSPMM_TUNE_P4_G
+#define CSRSPMM_TUNE_P4_G 32
+#endif
+#ifndef CSRSPMM_TUNE_P4_NV
+#define CSRSPMM_TUNE_P4_NV 4
+#endif
+#ifndef CSRSPMM_TUNE_P4_D
+#define CSRSPMM_TUNE_P4_D 4
+#endif
+
 // L2 residency hints: rows of B loaded with an evict_last policy applied to this percentage of
 // the lines, C written with streaming stores.  Both are OFF by default: on B200 neither helped
 // (config 3, B = 2.1 x L2: 685 us without hints, 687-714 us with any combination of them).
@@ -162,6 +221,13 @@ namespace csrspmm_b200 {
 struct ShapeDesc {
     int G, NV, TG;
 };
+struct PieceShapeDesc {
+    int G, NV, D;
+};
+constexpr PieceShapeDesc kPieceShapes[5] = {
+    {CSRSPMM_TUNE_P0_G, CSRSPMM_TUNE_P0_NV, CSRSPMM_TUNE_P0_D}, {CSRSPMM_TUNE_P1_G, CSRSPMM_TUNE_P1_NV, CSRSPMM_TUNE_P1_D},
+    {CSRSPMM_TUNE_P2_G, CSRSPMM_TUNE_P2_NV, CSRSPMM_TUNE_P2_D}, {CSRSPMM_TUNE_P3_G, CSRSPMM_TUNE_P3_NV, CSRSPMM_TUNE_P3_D},
+    {CSRSPMM_TUNE_P4_G, CSRSPMM_TUNE_P4_NV, CSRSPMM_TUNE_P4_D}};
 constexpr int kNumShapes = 5;
 constexpr ShapeDesc kShapes[kNumShapes] = {
     {CSRSPMM_TUNE_S0_G, CSRSPMM_TUNE_S0_NV, CSRSPMM_TUNE_S0_TG}, {CSRSPMM_TUNE_S1_G, CSRSPMM_TUNE_S1_NV, CSRSPMM_TUNE_S1_TG},

@@ -63,8 +63,55 @@ def workspace_bytes(M: int, Kd: int, Nd: int, nnz: int) -> int:
     return int(_lib.lib().csrspmm_b200_workspace_bytes(C.byref(a)))
 
 
+class Schedule:
+    """A per-matrix schedule (``csrspmm_b200_schedule_create``): the long rows of one sparsity pattern cut
+    into pieces ordered by slab of B, so that their gather is served from L2.  Built once from the CUDA
+    tensors ``row_ptr`` and ``col_idx``; valid while they are unchanged (values and B may change).  Pass it
+    to ``spmm`` / ``SpmmCall`` as ``schedule=``.  ``Kd`` and ``Nd`` are the sizes of the B it will multiply
+    (they size the slabs).  ``threshold`` / ``slab_rows`` / ``piece_nnz`` of 0 let the library choose."""
+
+    def __init__(self, row_ptr, col_idx, Kd: int, Nd: int, *, ldb: int | None = None, threshold: int = 0,
+                 slab_rows: int = 0, piece_nnz: int = 0):
+        if not (row_ptr.is_cuda and col_idx.is_cuda and row_ptr.dtype == torch.int32 and col_idx.dtype == torch.int32):
+            raise RuntimeError("a schedule is built from int32 CUDA row_ptr and col_idx")
+        self.L = _lib.lib()
+        self.device = row_ptr.device
+        M, n = row_ptr.numel() - 1, col_idx.numel()
+        a = _lib.make_args(M, int(Kd), int(Nd), n, row_ptr.data_ptr(), col_idx.data_ptr(), ldb=ldb or Nd)
+        opt = _lib.ScheduleOptions(C.sizeof(_lib.ScheduleOptions), int(threshold), int(slab_rows), int(piece_nnz))
+        handle = C.c_void_p(None)
+        with torch.cuda.device(self.device):
+            st = C.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
+            _lib.check(self.L.csrspmm_b200_schedule_create(C.byref(a), C.byref(opt), C.byref(handle), st),
+                       "csrspmm_b200_schedule_create")
+        self.handle = handle.value
+        self._keep = (row_ptr, col_idx)
+
+    def info(self) -> dict:
+        i = _lib.ScheduleInfo()
+        i.struct_size = C.sizeof(_lib.ScheduleInfo)
+        _lib.check(self.L.csrspmm_b200_schedule_info_get(C.c_void_p(self.handle), C.byref(i)), "csrspmm_b200_schedule_info_get")
+        return {k: getattr(i, k) for k, _ in _lib.ScheduleInfo._fields_ if k != "struct_size"}
+
+    @property
+    def active(self) -> bool:
+        """False when the schedule is empty (no long rows, B fits one slab, or unsorted columns)."""
+        return self.info()["long_rows"] > 0
+
+    def close(self):
+        if getattr(self, "handle", None):
+            self.L.csrspmm_b200_schedule_destroy(C.c_void_p(self.handle))
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
 def spmm(row_ptr, col_idx, values, B, C_out=None, alpha=1.0, beta=0.0, *, entry="naive", kernel="auto",
-         max_row_nnz=0, e2m1_scale=None, nnz=None, workspace=None, status_word=None, sync=False):
+         max_row_nnz=0, e2m1_scale=None, nnz=None, workspace=None, status_word=None, sync=False, schedule=None):
     """C_out = alpha * A @ B + beta * C_out on the current stream; returns C_out.
 
     C_out is allocated (uninitialised) when omitted, which requires beta == 0.  With
@@ -72,6 +119,7 @@ def spmm(row_ptr, col_idx, values, B, C_out=None, alpha=1.0, beta=0.0, *, entry=
     gives the element count.  ``kernel`` pins "row", "merge" or "tma".  ``workspace`` is an
     optional uint8 tensor of at least ``workspace_bytes(...)`` bytes; without it the scratch comes
     from torch's caching allocator.  ``sync=True`` waits and raises on device-side errors.
+    ``schedule`` is an optional ``Schedule`` built for this matrix.
     """
     packed = e2m1_scale is not None
     _check_csr(row_ptr, col_idx, values, B, packed)
@@ -101,16 +149,17 @@ def spmm(row_ptr, col_idx, values, B, C_out=None, alpha=1.0, beta=0.0, *, entry=
                        max_row_nnz=max_row_nnz,
                        value_format=_lib.VALUES_E2M1 if packed else _lib.VALUES_F32,
                        value_scale=float(e2m1_scale) if packed else 1.0,
-                       status_word=status_word.data_ptr() if status_word is not None else 0)
+                       status_word=status_word.data_ptr() if status_word is not None else 0,
+                       schedule=schedule.handle if schedule is not None else 0)
     with torch.cuda.device(B.device):
         if M > 0 and Nd > 0:
             chosen = L.csrspmm_b200_select_kernel(C.byref(a))
             if chosen < 0:
                 raise _lib.SpmmError(-chosen, "csrspmm_b200_select_kernel")
-            if chosen != _lib.KERNEL_ROW:
+            if chosen != _lib.KERNEL_ROW or schedule is not None:
                 need = int(L.csrspmm_b200_workspace_bytes(C.byref(a)))
                 if workspace is None or workspace.numel() * workspace.element_size() < need:
-                    workspace = torch.empty(need, dtype=torch.uint8, device=B.device)
+                    workspace = torch.empty(max(need, 256), dtype=torch.uint8, device=B.device)
                 a.workspace = workspace.data_ptr()
                 a.workspace_bytes = workspace.numel() * workspace.element_size()
         stream = torch.cuda.current_stream(B.device).cuda_stream
@@ -168,7 +217,7 @@ class SpmmCall:
     same operands); keeps its tensors alive."""
 
     def __init__(self, row_ptr, col_idx, values, B, C_out, alpha=1.0, beta=0.0, *, entry="naive", kernel="auto",
-                 max_row_nnz=0, e2m1_scale=None, nnz=None, workspace=None, status_word=None):
+                 max_row_nnz=0, e2m1_scale=None, nnz=None, workspace=None, status_word=None, schedule=None):
         packed = e2m1_scale is not None
         _check_csr(row_ptr, col_idx, values, B, packed)
         M, Kd, Nd = row_ptr.numel() - 1, B.size(0), B.size(1)
@@ -183,7 +232,8 @@ class SpmmCall:
             beta=beta, entry=_ENTRY[entry], kernel=_lib.KERNEL_IDS[kernel], max_row_nnz=max_row_nnz,
             value_format=_lib.VALUES_E2M1 if packed else _lib.VALUES_F32,
             value_scale=float(e2m1_scale) if packed else 1.0,
-            status_word=status_word.data_ptr() if status_word is not None else 0)
+            status_word=status_word.data_ptr() if status_word is not None else 0,
+            schedule=schedule.handle if schedule is not None else 0)
         self.kernel = "row"
         self.launches = 0
         if M > 0 and Nd > 0:
@@ -192,14 +242,17 @@ class SpmmCall:
                 raise _lib.SpmmError(-k, "csrspmm_b200_select_kernel")
             self.kernel = _lib.KERNEL_NAMES[k]
             self.launches = 1 if k == _lib.KERNEL_ROW else 2
-            if k != _lib.KERNEL_ROW:
+            if schedule is not None and schedule.active and kernel in ("auto", "merge"):
+                self.kernel = "scheduled"  # pieces, slot sums, merge-path over the other rows, fix-up
+                self.launches = 4
+            if k != _lib.KERNEL_ROW or self.kernel == "scheduled":
                 need = int(self.L.csrspmm_b200_workspace_bytes(C.byref(self.args)))
                 if workspace is None or workspace.numel() * workspace.element_size() < need:
-                    workspace = torch.empty(need, dtype=torch.uint8, device=B.device)
+                    workspace = torch.empty(max(need, 256), dtype=torch.uint8, device=B.device)
                 self.args.workspace = workspace.data_ptr()
                 self.args.workspace_bytes = workspace.numel() * workspace.element_size()
         self.workspace = workspace  # scratch of the split kernels (None for the row kernel); may be shared
-        self._keep = (row_ptr, col_idx, values, B, C_out, workspace, status_word)
+        self._keep = (row_ptr, col_idx, values, B, C_out, workspace, status_word, schedule)
         self._ref = C.byref(self.args)
         self.out = C_out
 

@@ -23,6 +23,8 @@
  *   csrspmm_b200_select_kernel  the (stub) auto-selection in src/csrspmm.cpp:34-40
  *   csrspmm_b200_dense2csr_count/_fill, _csr2dense   csrspmm::dense2csr / csr2dense,
  *                               src/host/csr_utils.cpp:70-145, on device-resident matrices
+ *   csrspmm_b200_schedule_create/_destroy/_info   the per-matrix analysis the reference's spmm()
+ *                               leaves as a stub (src/csrspmm.cpp:34-40: both branches pick Naive)
  *   validate / row_stats / partition_rows / e2m1_*   no counterpart in the reference
  */
 #ifndef CSRSPMM_B200_H
@@ -35,7 +37,7 @@
 extern "C" {
 #endif
 
-#define CSRSPMM_B200_ABI_VERSION 1
+#define CSRSPMM_B200_ABI_VERSION 2
 
 /* Same handle type as cudaStream_t; NULL is the legacy default stream. */
 typedef struct CUstream_st* csrspmm_b200_stream_t;
@@ -106,6 +108,9 @@ typedef struct csrspmm_b200_args {
                                takes it from the stream-ordered allocator for this call */
     size_t workspace_bytes; /* size of workspace when it is not NULL */
     int32_t* status_word;   /* optional device int32 the kernels OR error bits into */
+    const struct csrspmm_b200_schedule* schedule; /* optional: a schedule built for this matrix by
+                               csrspmm_b200_schedule_create (device-pointer entry points only); NULL
+                               multiplies without one */
 } csrspmm_b200_args;
 
 int csrspmm_b200_abi_version(void);
@@ -154,8 +159,8 @@ int csrspmm_b200_copy_rows(void* dst, size_t dst_pitch_bytes, const void* src, s
  * a plug-in whose host forbids allocation calls, a loop that must never enter the allocator.  It
  * always runs the merge-path kernel and keeps that kernel's scratch in a fixed array inside the
  * library's device image (CSRSPMM_B200_NOALLOC_SCRATCH_BYTES per GPU, held until the process
- * ends), so it calls no allocation routine at all.  args.kernel / workspace / workspace_bytes are
- * ignored.  A problem whose scratch (an int32 and a row of Nd floats per 1536..3072 of M + nnz)
+ * ends), so it calls no allocation routine at all.  args.kernel / workspace / workspace_bytes /
+ * schedule are ignored.  A problem whose scratch (an int32 and a row of Nd floats per CTA of the merge kernel, i.e. per 512..3072 of M + nnz)
  * does not fit is refused with ERR_WORKSPACE and nothing is launched.  Every call on a device
  * shares the one array: the previous call's contents are harmless (every slot that is read is
  * rewritten first by the same call), but two calls running on the GPU at the same time corrupt
@@ -191,6 +196,59 @@ size_t csrspmm_b200_workspace_bytes(const csrspmm_b200_args* args);
  * returns a csrspmm_b200_kernel, or a negative csrspmm_b200_status on bad arguments.
  * The environment variable CSRSPMM_FORCE_KERNEL=row|merge|tma overrides AUTO. */
 int csrspmm_b200_select_kernel(const csrspmm_b200_args* args);
+
+/* ---- per-matrix schedule ---------------------------------------------------------------------
+ * Stands where the reference's spmm() has a stub that inspects nothing (src/csrspmm.cpp:34-40).
+ * For a matrix whose B is several times larger than L2 the gather of B rows is what the product
+ * costs, and rows long enough to hold several entries per L2-sized slab of B can take that gather
+ * from L2 instead of HBM if their work is ordered by slab.  A schedule is that ordering, built once
+ * per matrix from row_ptr and col_idx (never the values) on the device:
+ *   - rows of `long_row_threshold` entries or more are "long"; the columns of every long row must
+ *     be ascending (else the schedule is built empty and changes nothing);
+ *   - each long row is cut at the slab boundaries (slabs of `slab_rows` columns of A = rows of B)
+ *     and every cut piece again into pieces of at most `piece_nnz` entries; the pieces are listed
+ *     slab by slab, so that CTAs resident together gather from the same slab of B;
+ *   - a product with args.schedule set runs three kernels: the pieces (each one sequential fp32
+ *     sum into its own slot of scratch), the per-row sum of the slots in stored order (no atomics:
+ *     the result is the same on every run), and the merge-path kernel over the remaining rows.
+ * The schedule holds device memory (csrspmm_b200_schedule_info.device_bytes) on the device that
+ * was current at creation and must be used there.  It describes the sparsity pattern only: keep it
+ * as long as row_ptr and col_idx are unchanged (values, B, C, alpha, beta and Nd may change; Nd
+ * only moves the slab size away from the one planned).  A call whose M, Kd or nnz differ from the
+ * schedule's is refused with ERR_BAD_ARG.  args.kernel must be AUTO or MERGE and args.row_ptr_base
+ * 0.  Scratch: csrspmm_b200_workspace_bytes(args) with args.schedule set.  Thread-safe for
+ * concurrent products as long as each has its own workspace. */
+struct csrspmm_b200_schedule;
+typedef struct csrspmm_b200_schedule csrspmm_b200_schedule;
+
+typedef struct csrspmm_b200_schedule_options {
+    uint32_t struct_size;       /* sizeof(csrspmm_b200_schedule_options) */
+    int32_t long_row_threshold; /* rows of this many entries or more are scheduled; 0 = choose */
+    int32_t slab_rows;          /* rows of B per slab; 0 = choose (about 32 MiB of B) */
+    int32_t piece_nnz;          /* longest piece one lane group accumulates; 0 = choose */
+} csrspmm_b200_schedule_options;
+
+typedef struct csrspmm_b200_schedule_info {
+    uint32_t struct_size; /* set by the caller: sizeof(csrspmm_b200_schedule_info) */
+    int32_t M, Kd, Nd;
+    int64_t nnz;
+    int32_t long_row_threshold, slab_rows, num_slabs, piece_nnz;
+    int32_t long_rows;     /* rows the schedule covers (0: an empty schedule, plain kernels run) */
+    int64_t long_nnz;      /* their entries */
+    int64_t pieces;        /* work items = scratch slots of Nd floats each */
+    int32_t columns_sorted; /* 0 when a long row with unsorted columns emptied the schedule */
+    size_t device_bytes;   /* device memory the schedule keeps */
+    double build_ms;       /* wall time of csrspmm_b200_schedule_create */
+} csrspmm_b200_schedule_info;
+
+/* Device row_ptr / col_idx in args (values, B, C are not touched; Nd and ldb size the slabs).
+ * options may be NULL.  Synchronous: returns when the schedule is complete.  The environment
+ * variables CSRSPMM_SCHED_THRESHOLD, CSRSPMM_SCHED_SLAB_MIB and CSRSPMM_SCHED_PIECE override
+ * zero fields of the options. */
+int csrspmm_b200_schedule_create(const csrspmm_b200_args* args, const csrspmm_b200_schedule_options* options,
+                                 csrspmm_b200_schedule** out, csrspmm_b200_stream_t stream);
+int csrspmm_b200_schedule_destroy(csrspmm_b200_schedule* schedule);
+int csrspmm_b200_schedule_info_get(const csrspmm_b200_schedule* schedule, csrspmm_b200_schedule_info* info);
 
 /* ---- CSR validation (new; the reference validates nothing) ---------------------------------- */
 

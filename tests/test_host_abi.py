@@ -16,7 +16,7 @@ ROOT = Path(__file__).resolve().parents[1]
 
 def test_library_loads_and_exports_every_declared_symbol():
     L = _lib.lib()
-    assert L.csrspmm_b200_abi_version() == 1
+    assert L.csrspmm_b200_abi_version() == _lib.ABI_VERSION == 2
     header = (ROOT / "include" / "csrspmm_b200.h").read_text()
     declared = set(re.findall(r"^(?:int|int32_t|size_t|float|const char\*)\s+(csrspmm_b200_[a-z0-9_]+)\(", header, re.M))
     assert declared == set(_lib.EXPORTED_SYMBOLS)
@@ -44,7 +44,7 @@ def test_cpp_api_symbols_exported():
 def test_args_struct_layout_is_checked():
     L = _lib.lib()
     a = _lib.make_args(4, 4, 4, 4)
-    assert C.sizeof(_lib.Args) == 136
+    assert C.sizeof(_lib.Args) == 144
     assert L.csrspmm_b200_select_kernel(C.byref(a)) > 0
     a.struct_size = 8
     assert L.csrspmm_b200_select_kernel(C.byref(a)) == -_lib.ERR_BAD_ARG
@@ -102,6 +102,39 @@ def test_force_kernel_environment(monkeypatch):
     monkeypatch.setenv("CSRSPMM_FORCE_KERNEL", "tma")
     assert ops.selected_kernel(100, 100, 66, 1000, max_row_nnz=12) == "row"  # cannot run -> AUTO
     assert ops.selected_kernel(100, 100, 64, 1000, kernel="row") == "row"    # explicit pin wins
+
+
+def test_host_round_trip_scratch_covers_every_row_block():
+    """spmm_host multiplies row blocks out of one scratch area.  A block can fall under the merge kernel's
+    small-problem threshold (smaller tiles, more carry rows) although the whole matrix does not: the arena
+    must be sized for that."""
+    M, Kd, Nd, nnz = 40000, 40000, 512, 420000
+    L = _lib.lib()
+    whole = _lib.make_args(M, Kd, Nd, nnz)
+    al = lambda v: -(-v // 256) * 256
+    others = al((M + 1) * 4) + al(nnz * 4) + al(nnz * 4) + al(Kd * Nd * 4) + al(M * Nd * 4) + 256
+    scratch = L.csrspmm_b200_host_arena_bytes(C.byref(whole)) - others
+    # a block that holds a hub row of 200 000 entries and little else
+    block = _lib.make_args(100, Kd, Nd, 200300, kernel=_lib.KERNEL_MERGE)
+    assert L.csrspmm_b200_workspace_bytes(C.byref(block)) <= scratch
+    assert L.csrspmm_b200_workspace_bytes(C.byref(whole)) <= scratch
+
+
+def test_schedule_entry_points_reject_bad_arguments_before_any_cuda_call():
+    L = _lib.lib()
+    a = _lib.make_args(8, 8, 4, 10, row_ptr=256, col_idx=256)
+    h = C.c_void_p(None)
+    assert L.csrspmm_b200_schedule_create(C.byref(a), None, None, None) == _lib.ERR_BAD_ARG
+    bad = _lib.ScheduleOptions(4, 0, 0, 0)
+    assert L.csrspmm_b200_schedule_create(C.byref(a), C.byref(bad), C.byref(h), None) == _lib.ERR_BAD_ARG
+    a.row_ptr_base = 2
+    assert L.csrspmm_b200_schedule_create(C.byref(a), None, C.byref(h), None) == _lib.ERR_BAD_ARG
+    a.row_ptr_base, a.row_ptr = 0, None
+    assert L.csrspmm_b200_schedule_create(C.byref(a), None, C.byref(h), None) == _lib.ERR_BAD_ARG
+    assert h.value is None
+    assert L.csrspmm_b200_schedule_destroy(None) == _lib.OK
+    info = _lib.ScheduleInfo()
+    assert L.csrspmm_b200_schedule_info_get(None, C.byref(info)) == _lib.ERR_BAD_ARG
 
 
 def test_workspace_depends_on_sizes_only():
