@@ -45,6 +45,11 @@ void fill_params(const csrspmm_b200_args* a, const Plan& plan, SpmmParams* out)
     p.alpha = a->alpha;
     p.beta = a->beta;
     p.status_word = a->status_word;
+    // CSRSPMM_TEST_WAIT_LIMIT=<n> (tests only): a wait on a row copy gives up after n attempts, so the
+    // give-up path can be exercised without anything being stuck (the drain wait keeps the full limit)
+    p.wait_limit = kWaitSpinLimit;
+    if (const char* e = std::getenv("CSRSPMM_TEST_WAIT_LIMIT"))
+        if (*e != 0) p.wait_limit = (unsigned)std::strtoul(e, nullptr, 10);
     *out = p;
 }
 
@@ -515,6 +520,10 @@ int csrspmm_b200_spmm_host(const csrspmm_b200_args* a, void* device_arena, size_
     cudaEvent_t done[kMaxBlocks] = {};
     int events = 0;
     auto cleanup = [&]() {
+        // also the way out of every failure below: nothing may still be copying into or out of the
+        // arena, or into this frame's `word`, when they go away (errors of these waits are ignored)
+        cudaStreamSynchronize(st);
+        if (copy_stream) cudaStreamSynchronize(copy_stream);
         for (int k = 0; k < events; ++k) cudaEventDestroy(done[k]);
         if (copy_stream) cudaStreamDestroy(copy_stream);
         if (owned) cudaFreeAsync(arena, st);

@@ -9,9 +9,12 @@
 #include <csrspmm/error_check.h>
 #include <csrspmm/spmm_launcher.cuh>
 
+#include <cuda_runtime.h>
+
 #include <cstdio>
 #include <cstdlib>
 #include <iostream>
+#include <mutex>
 
 #include "csrspmm_b200.h"
 
@@ -20,6 +23,45 @@ namespace csrspmm {
 namespace {
 
 thread_local int g_last_launch_status = CSRSPMM_B200_OK;
+
+// The longest row of a device-resident matrix, measured once (one small kernel and a host read on
+// the legacy default stream) and remembered per (device, row_ptr address, rows, nnz).  It steers
+// the kernel choice only: a matrix whose rows are known to be even takes the whole-row kernel,
+// anything else the merge-path kernel.  CSRMatrix::max_row_nnz is the caller's claim -- the
+// reference's wrappers leave it unset on three of five ops
+// (torch_csrspmm/torch_csrspmm_warp_per_row.cpp:34-40) and a stale value would send a skewed matrix
+// to the whole-row kernel -- so it is used only when measuring fails.  A stale cache entry (another
+// matrix of the same size placed at the same address) costs speed, never correctness.
+struct RowStatsEntry {
+    int device;
+    const int* row_ptr;
+    int rows;
+    int nnz;
+    int longest;
+};
+constexpr int kRowStatsEntries = 64;
+std::mutex g_row_stats_mutex;
+RowStatsEntry g_row_stats[kRowStatsEntries] = {};
+int g_row_stats_next = 0;
+
+int longest_row_of(const CSRMatrix& A)
+{
+    if (A.height <= 0 || A.nnz <= 0 || A.row_ptr == nullptr) return 0;
+    int device = -1;
+    if (cudaGetDevice(&device) != cudaSuccess) return A.max_row_nnz;
+    {
+        std::lock_guard<std::mutex> lock(g_row_stats_mutex);
+        for (const RowStatsEntry& e : g_row_stats)
+            if (e.row_ptr == A.row_ptr && e.device == device && e.rows == A.height && e.nnz == A.nnz) return e.longest;
+    }
+    int64_t stats[4] = {0, 0, 0, 0};
+    if (csrspmm_b200_row_stats_device(A.height, A.row_ptr, stats, nullptr) != CSRSPMM_B200_OK) return A.max_row_nnz;
+    const int longest = stats[0] > 0x7fffffff ? 0x7fffffff : (int)stats[0];
+    std::lock_guard<std::mutex> lock(g_row_stats_mutex);
+    g_row_stats[g_row_stats_next] = RowStatsEntry{device, A.row_ptr, A.height, A.nnz, longest};
+    g_row_stats_next = (g_row_stats_next + 1) % kRowStatsEntries;
+    return longest;
+}
 
 void launch(const CSRMatrix& A, const DenseMatrix& B, DenseMatrix& C, float alpha, float beta,
             csrspmm_b200_entry entry)
@@ -43,7 +85,7 @@ void launch(const CSRMatrix& A, const DenseMatrix& B, DenseMatrix& C, float alph
     a.beta = beta;
     a.entry = entry;
     a.kernel = CSRSPMM_B200_KERNEL_AUTO;
-    a.max_row_nnz = A.max_row_nnz;
+    a.max_row_nnz = longest_row_of(A);
     const int status = csrspmm_b200_spmm(&a, nullptr);  // legacy default stream, like the reference
     g_last_launch_status = status;
     if (status != CSRSPMM_B200_OK)

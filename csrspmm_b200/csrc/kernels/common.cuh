@@ -19,6 +19,9 @@ constexpr int kStatusBadTile = 1;      // merge-path coordinates inconsistent (m
 constexpr int kStatusColClamped = 2;   // a column index outside [0, Kd) was clamped
 constexpr int kStatusWaitTimeout = 4;  // a bounded wait on an mbarrier gave up
 
+// Attempts of a bounded wait before it gives up (each attempt is itself a short hardware wait).
+constexpr unsigned kWaitSpinLimit = 1u << 22;
+
 constexpr int kValuesF32 = 0;
 constexpr int kValuesE2M1 = 1;
 
@@ -45,6 +48,7 @@ struct SpmmParams {
     float* carry_val;    // one row of carry_ld floats per tile
     long long carry_ld;  // multiple of 4
     int* status_word;    // may be null
+    unsigned wait_limit; // bulk-copy kernel: attempts a wait on a row copy makes before it gives up
     int skip_len;        // merge kernel with SKIP: rows of this many entries or more are left to the
                          // scheduled pieces (neither summed nor written); 0 = every row is mine
 };

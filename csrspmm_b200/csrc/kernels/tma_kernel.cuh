@@ -23,7 +23,6 @@
 namespace csrspmm_b200 {
 
 constexpr int kTmaWarps = kMergeThreads / 32;
-constexpr unsigned kWaitSpinLimit = 1u << 22;
 
 __device__ __forceinline__ unsigned smem_u32(const void* p)
 {
@@ -55,9 +54,9 @@ __device__ __forceinline__ bool mbar_try_wait(unsigned bar, unsigned parity)
 }
 
 // false when the limit was reached
-__device__ __forceinline__ bool mbar_wait_bounded(unsigned bar, unsigned parity)
+__device__ __forceinline__ bool mbar_wait_bounded(unsigned bar, unsigned parity, unsigned limit = kWaitSpinLimit)
 {
-    for (unsigned spin = 0; spin < kWaitSpinLimit; ++spin)
+    for (unsigned spin = 0; spin < limit; ++spin)
         if (mbar_try_wait(bar, parity)) return true;
     return false;
 }
@@ -167,7 +166,7 @@ __global__ void __launch_bounds__(kMergeThreads, CSRSPMM_TUNE_TMA_MINB) spmm_tma
         const int slot = k % SLOTS;
         const unsigned parity = (unsigned)(k / SLOTS) & 1u;
         // the vote keeps the warp together should the limit be hit by some lanes only
-        if (!__all_sync(0xffffffffu, mbar_wait_bounded(bar_base + slot * 8u, parity))) {
+        if (!__all_sync(0xffffffffu, mbar_wait_bounded(bar_base + slot * 8u, parity, p.wait_limit))) {
             failed = true;
             break;
         }
@@ -199,15 +198,16 @@ __global__ void __launch_bounds__(kMergeThreads, CSRSPMM_TUNE_TMA_MINB) spmm_tma
     }
     failed = __any_sync(0xffffffffu, failed);
     if (failed) {
-        // drain: copies k .. issued-1 may still be landing in this CTA's shared memory
+        // drain: copies k .. issued-1 may still be landing in this CTA's shared memory; this wait keeps
+        // the full limit whatever p.wait_limit is, so that no copy can arrive after the CTA has gone
         if (lane == 0) report_status(p, kStatusWaitTimeout);
         for (int q = k; q < issued; ++q) mbar_wait_bounded(bar_base + (q % SLOTS) * 8u, (unsigned)(q / SLOTS) & 1u);
-        dirty = false;  // publish nothing from a failed range
+        dirty = false;  // publish nothing from a failed range: no carry, and the held-back first row stays unwritten
     } else {
         while (i < r.il1) finish_row();
     }
 
-    merge_tile_finish<Smem, G, NV, VW>(p, s, r, 0, g, lane, acc, head, dirty);
+    merge_tile_finish<Smem, G, NV, VW>(p, s, r, 0, g, lane, acc, head, dirty, failed);
 }
 
 }  // namespace csrspmm_b200

@@ -299,8 +299,10 @@ def _longest_row_hint(row_ptr) -> int:
 
 def _op(entry, row_ptr, col_idx, values, B, alpha, beta, max_row_nnz=0):
     del beta
-    if int(max_row_nnz) <= 0 and row_ptr.is_cuda and row_ptr.dtype == torch.int32:
-        max_row_nnz = _longest_row_hint(row_ptr)  # the reference's non-smem ops carry no such argument
+    if row_ptr.is_cuda and row_ptr.dtype == torch.int32:
+        # measured, not believed: three of the reference's five ops carry no such argument, and a stale value
+        # passed to the other two would send a skewed matrix to the whole-row kernel
+        max_row_nnz = _longest_row_hint(row_ptr)
     return spmm(row_ptr, col_idx, values, B, None, float(alpha), 0.0, entry=entry, max_row_nnz=int(max_row_nnz))
 
 

@@ -31,7 +31,8 @@ _u8p = C.POINTER(C.c_uint8)
 def build(with_ref: bool | None = None) -> None:
     """Compile the oracle (and the reference cross-check when its checkout is present)."""
     targets = ["all"]
-    ref_root = os.environ.get("CSRSPMM_REFERENCE", "/root/reference")
+    # the reference checkout: CSRSPMM_REFERENCE, else a checkout next to this repository
+    ref_root = os.environ.get("CSRSPMM_REFERENCE") or str(_HERE.parents[1] / "reference")
     if with_ref is None:
         with_ref = Path(ref_root, "src", "host", "dense_utils.cpp").exists()
     if with_ref:
@@ -39,6 +40,7 @@ def build(with_ref: bool | None = None) -> None:
         targets.append("refgpu")
         if (_HERE.parent / "csrspmm_b200" / "lib" / "libcsrspmm_b200.so").exists():
             targets.append("dropin")
+            targets.append("pyext")
     subprocess.run(["make", "-s", "-C", str(_HERE), f"REFERENCE={ref_root}", *targets], check=True)
 
 

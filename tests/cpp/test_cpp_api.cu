@@ -4,6 +4,7 @@
 // integer and real-valued data, and with a non-zero exit code on any failure.
 #include <cstdio>
 #include <cstdlib>
+#include <cmath>
 #include <cstring>
 #include <string>
 
@@ -24,6 +25,13 @@ static int failures = 0;
             ++failures;                                                     \
         }                                                                   \
     } while (0)
+
+static bool all_finite(const DenseMatrix& m)
+{
+    for (size_t k = 0; k < size_t(m.height) * size_t(m.width); ++k)
+        if (!std::isfinite(m.data[k])) return false;
+    return true;
+}
 
 static void run_case(int M, int N, int K, float sparsity, float alpha, float beta, bool integer_values)
 {
@@ -90,7 +98,8 @@ static void run_case(int M, int N, int K, float sparsity, float alpha, float bet
         // integer data: every sum is exact in fp32; real data: accumulation-order tolerance
         // scaled by the magnitude of the sums (|a|,|b| <= 10, up to N terms)
         const float tol = integer_values ? 1e-2f : 1e-5f * 100.0f * float(N) + 1e-6f;
-        const bool ok = dense_compare(hOut, hRef, tol);
+        // dense_compare keeps the reference's test (fabs(a-b) > tol, false for NaN), so finiteness is checked here
+        const bool ok = dense_compare(hOut, hRef, tol) && all_finite(hOut);
         std::printf("%-18s %dx%dx%d s=%.2f a=%.2f b=%.2f int=%d nnz=%d max_row=%d : %s\n", name, M, N, K,
                     sparsity, alpha, beta, int(integer_values), hA_csr.nnz, hA_csr.max_row_nnz,
                     ok ? "ok" : "MISMATCH");
@@ -107,6 +116,7 @@ static void run_case(int M, int N, int K, float sparsity, float alpha, float bet
         cudaCheck(cudaDeviceSynchronize());
         dense_device2host(dC, hOut);
         EXPECT(dense_compare(hOut, hRef, integer_values ? 1e-2f : 1e-5f * 100.0f * float(N) + 1e-6f));
+        EXPECT(all_finite(hOut));
         dense_free_host(hOut);
         dense_free_device(dC);
     }

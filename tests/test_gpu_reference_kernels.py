@@ -72,6 +72,35 @@ def test_results_equal_the_reference_kernels(cuda_lib, name, p):
     assert torch.allclose(C_our, C_ref, rtol=1e-5, atol=1e-6)
 
 
+@pytest.mark.parametrize("scale", [16, 1])
+def test_packed_e2m1_against_the_reference_fp4_kernels(cuda_lib, scale):
+    """BASELINE config 4 (full size and 1/16): values quantised with this library's e2m1 codec, the DECODED
+    fp32 values fed to the reference's own WarpPerRowFp4 / WarpPerRowSmemFp4 GPU kernels
+    (src/device/csrspmm_warp_per_row_fp4.cu:9-65, csrspmm_warp_per_row_smem_fp4.cu:11-84: "Fp4" is float4,
+    the values are fp32), the packed codes fed to this library.  Identical decoded operands and one fp32
+    accumulator per output in stored order on both sides: the whole-row kernel must agree bit for bit, the
+    split kernels within rel 1e-4 of the reference kernel (magnitude-scaled, as for every cut row)."""
+    ref = oracle.ReferenceGpu()
+    p = G.make("cfg4_fp4", scale=scale)
+    rp, ci, va, B = _dev(p)
+    mx = int(np.diff(p.row_ptr).max())
+    packed, e2m1_scale = ops.e2m1_quantize(va)
+    decoded = ops.e2m1_dequantize(packed, p.nnz, e2m1_scale)
+    assert torch.equal(decoded.cpu(), torch.from_numpy(oracle.e2m1_decode(packed.cpu().numpy(), p.nnz, e2m1_scale)))
+    mag = torch.zeros(p.M, p.Nd, device="cuda")  # sum |a*b| per output, for the scaled bound
+    ops.spmm(rp, ci, decoded.abs(), B.abs(), mag, kernel="row", max_row_nnz=mx, sync=True)
+    for algo in ("WarpPerRowFp4", "WarpPerRowSmemFp4"):
+        C_ref = torch.full((p.M, p.Nd), float("nan"), device="cuda")
+        assert ref.spmm(algo, rp, ci, decoded, B, C_ref, 1.0, 0.0, mx) == 0
+        torch.cuda.synchronize()
+        got = ops.spmm(rp, ci, packed, B, kernel="row", max_row_nnz=mx, e2m1_scale=e2m1_scale, nnz=p.nnz, sync=True)
+        assert torch.equal(got, C_ref), f"{algo}: packed whole-row kernel differs by {float((got - C_ref).abs().max())}"
+        for k in ("merge", "tma"):
+            got = ops.spmm(rp, ci, packed, B, kernel=k, e2m1_scale=e2m1_scale, nnz=p.nnz, sync=True)
+            assert bool(((got - C_ref).abs() <= 1e-4 * mag + 1e-6).all()), f"{algo} vs packed {k}"
+            assert float(torch.isclose(got, C_ref, rtol=1e-4, atol=1e-6).float().mean()) > 0.999
+
+
 def test_reference_limits_are_not_ours(cuda_lib):
     """Shapes the reference's kernels cannot launch (or would address out of range) run here."""
     ref = oracle.ReferenceGpu()
