@@ -44,25 +44,27 @@ sys.path.insert(0, str(ROOT))
 L2_BYTES = 126 * 2 ** 20
 FALLBACK_HBM_GBS = 6650.0
 
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu
-# captures summarised under profiles/ (bytes; None = not captured yet)
-NCU_TRAFFIC = {
-    # (workload, kernel): (bytes per launch in the capture, non-zeros of the captured case)
-    ("cfg3_powerlaw", "merge"): (3.641e9, 16802627),   # full size, profiles/merge_kernel_cfg3_powerlaw.md
-    ("cfg5_xl", "tma"): (32.88e9, 16777248),           # 1/8 of the rows, profiles/tma_and_merge_kernel_cfg5_xl_eighth.md
-    ("cfg5_xl", "merge"): (32.96e9, 16777248),         # 1/8 of the rows, same file
-    ("cfg2_medium", "row"): (10.6e6, 268783),          # profiles/row_kernel_cfg2_medium_and_cfg4.md
-    ("cfg4_fp4", "row"): (0.977e9, 21471764),          # same file
-}
+# nominal fp32 multiply-add rate of a B200 (148 SMs x 128 lanes x 2 flops at the maximum SM clock): the
+# denominator of the "fraction of fp32-FMA peak" reported for compute/L2-bound configurations
+FP32_FMA_PEAK_TFLOPS = 148 * 128 * 2 * 1.965e9 / 1e12
 
 
 def ncu_traffic(workload, kernel, nnz):
-    """DRAM bytes per launch from the committed ncu capture, scaled by the non-zero count when the
-    captured case was smaller than (or a different shard of) what is being timed."""
-    ent = NCU_TRAFFIC.get((workload.split("/")[0], kernel))
-    if ent is None:
+    """DRAM bytes per step (dram__bytes_read.sum + dram__bytes_write.sum over the step's kernels) from
+    the ncu captures recorded in profiles/ncu_traffic.json, scaled by the non-zero count when the
+    captured case was smaller than (or a different shard of) what is being timed.  Each record names the
+    kernel instantiations it was taken from, so a stale record can be told from the launch list."""
+    f = ROOT / "profiles" / "ncu_traffic.json"
+    try:
+        recs = json.loads(f.read_text())["captures"]
+    except Exception:
         return None
-    return ent[0] * (nnz / ent[1])
+    for r in recs:
+        if r["workload"] == workload.split("/")[0] and r["kernel"] == kernel:
+            return {"bytes": r["dram_bytes_per_step"] * (nnz / r["nnz"]), "captured_nnz": r["nnz"],
+                    "kernels": r["kernels"], "summary": r["summary"],
+                    "lts_throughput_pct": r.get("lts_throughput_pct"), "l2_hit_rate_pct": r.get("l2_hit_rate_pct")}
+    return None
 
 
 def measured_peak():
@@ -141,9 +143,10 @@ def physical_gpu_index(local_index: int) -> int:
 
 # ---------------------------------------------------------------------------------------------------
 
-def time_spmm(torch, ops, t, C_out, workspace, kernel, steps, warmup, flush_buf, max_row_nnz=0, e2m1=None):
+def time_spmm(torch, ops, t, C_out, workspace, kernel, steps, warmup, flush_buf, max_row_nnz=0, e2m1=None,
+              schedule=None):
     """Runs warmup + steps SpMMs; returns seconds per step on this device."""
-    kw = dict(kernel=kernel, workspace=workspace, max_row_nnz=max_row_nnz)
+    kw = dict(kernel=kernel, workspace=workspace, max_row_nnz=max_row_nnz, schedule=schedule)
     if e2m1 is not None:
         kw.update(e2m1_scale=e2m1[1], nnz=e2m1[2])
     vals = e2m1[0] if e2m1 is not None else t["values"]
@@ -219,6 +222,65 @@ def launch_bound_modes(torch, ops, t, C_out, workspace, kernel, max_row_nnz, flu
 def problem_bytes(G, t, M, Nd, nnz, Kd, value_bytes=4.0):
     touched = G.touched_rows(t["col_idx"], Kd) if nnz else 0
     return G.min_bytes(M, Nd, nnz, touched, 0.0, value_bytes), touched
+
+
+def tolerance_report(torch, oracle, row_ptr, col_idx, values, B, C_dev, n_random=4096, n_long=64, seed=0):
+    """Rows [n_long longest + n_random random] of a device result against the CPU oracle: the strict
+    elementwise pass rate at rtol 1e-5 / atol 1e-6 against the sequential fp32 (fused multiply-add) oracle,
+    and the worst |err| / (1e-5 * sum|a*b| + 1e-6) against the fp64 oracle (<= 1 means inside the
+    accumulation-order bound)."""
+    rp_l = row_ptr.cpu().numpy().astype(np.int64)
+    M = rp_l.shape[0] - 1
+    lens = np.diff(rp_l)
+    rows = np.unique(np.concatenate([np.random.default_rng(seed).integers(0, M, n_random), np.argsort(lens)[-n_long:]]))
+    idx = np.concatenate([np.arange(rp_l[r], rp_l[r + 1]) for r in rows]) if rows.size else np.zeros(0, np.int64)
+    idx_d = torch.from_numpy(idx).to(col_idx.device)
+    uniq, inv = torch.unique(col_idx[idx_d].long(), return_inverse=True)
+    sub_rp = np.zeros(len(rows) + 1, np.int32)
+    np.cumsum(lens[rows], out=sub_rp[1:])
+    sub_ci = inv.to(torch.int32).cpu().numpy()
+    sub_va = values[idx_d].cpu().numpy()
+    sub_B = B[uniq].cpu().numpy() if uniq.numel() else np.zeros((1, B.shape[1]), np.float32)
+    th = oracle.max_threads()
+    f64, mag = oracle.spmm_f64(sub_rp, sub_ci, sub_va, sub_B, threads=th)
+    f32 = oracle.spmm(sub_rp, sub_ci, sub_va, sub_B, fused=True, threads=th)
+    got = C_dev[torch.from_numpy(rows).to(C_dev.device)].cpu().numpy()
+    bound = 1e-5 * mag + 1e-6
+    worst = float((np.abs(got - f64) / bound).max()) if got.size else 0.0
+    strict = np.isclose(got, f32, rtol=1e-5, atol=1e-6)
+    return {"rows_checked": int(rows.size), "longest_row_checked": int(lens[rows].max()) if rows.size else 0,
+            "strict_pass_rate_rtol1e-5_atol1e-6": float(strict.mean()) if strict.size else 1.0,
+            "bit_identical_to_fp32_oracle": float((got == f32).mean()) if got.size else 1.0,
+            "worst_err_over_bound": worst, "within_bound": bool(worst <= 1.0)}
+
+
+def copy_ceiling(torch, dev, barrier, D, nbytes=1 << 30, reps=3):
+    """What the host link of this box gives with nothing else going on: every rank copies `nbytes` of pinned
+    memory up and `nbytes` down at the same time (two streams), all ranks together.  GB/s per rank and
+    direction = nbytes / (slowest rank's time for both copies to finish)."""
+    h_up = torch.empty(nbytes, dtype=torch.uint8, pin_memory=True)
+    h_dn = torch.empty(nbytes, dtype=torch.uint8, pin_memory=True)
+    d_up = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+    d_dn = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+    s1, s2 = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+    best = {"both": float("inf"), "up": float("inf"), "down": float("inf")}
+    for mode in ("both", "up", "down"):
+        for _ in range(reps + 1):
+            barrier()
+            t0 = time.perf_counter()
+            if mode in ("both", "up"):
+                with torch.cuda.stream(s1):
+                    d_up.copy_(h_up, non_blocking=True)
+            if mode in ("both", "down"):
+                with torch.cuda.stream(s2):
+                    h_dn.copy_(d_dn, non_blocking=True)
+            s1.synchronize()
+            s2.synchronize()
+            best[mode] = min(best[mode], D.max_over_ranks(time.perf_counter() - t0, dev))
+    del h_up, h_dn, d_up, d_dn
+    g = nbytes / 1e9
+    return {"bytes_each_way_per_rank": nbytes, "GBps_per_rank_up_alone": g / best["up"], "GBps_per_rank_down_alone": g / best["down"],
+            "GBps_per_rank_each_way_together": g / best["both"]}
 
 
 def cusparse_via_torch(torch, t, M, Kd, steps, warmup, flush_buf):
@@ -361,9 +423,11 @@ def main(argv=None):
     ap.add_argument("--scale", type=int, default=1, help="divide M and Kd (for quick runs and ncu captures)")
     ap.add_argument("--kernel", default="auto", choices=["auto", "row", "merge", "tma"])
     ap.add_argument("--no-extras", action="store_true", help="skip e2e, cpu_baseline and other_workloads")
+    ap.add_argument("--no-schedule", action="store_true", help="never build a per-matrix schedule (plain AUTO kernel)")
     ap.add_argument("--only-e2e", action="store_true",
                     help="keep e2e but skip the oracle check, cpu_baseline, cuSPARSE and other_workloads")
     ap.add_argument("--e2e-steps", type=int, default=5)
+    ap.add_argument("--no-copy-ceiling", action="store_true", help="skip the copies-only measurement of the host link")
     ap.add_argument("--e2e-panels", type=int, default=0,
                     help="column panels of the host round trip (0 = the library's rule, 1 = no panels)")
     ns = ap.parse_args(argv)
@@ -433,6 +497,19 @@ def main(argv=None):
     flush_buf = torch.empty(2 * L2_BYTES, dtype=torch.uint8, device=dev) if flush else None
     chosen = ops.selected_kernel(my_rows, Kd, Nd, my_nnz, kernel=ns.kernel, max_row_nnz=0)
     launches_per_step = 1 if chosen == "row" else 2
+    # per-matrix schedule (built once per matrix, outside the timed region, like cuSPARSE's preprocess): the
+    # library decides by itself whether this matrix and this width of B are worth one
+    schedule, sched_info = None, None
+    if ns.kernel == "auto" and not ns.no_schedule and my_rows > 0:
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        schedule = ops.Schedule(t["row_ptr"], t["col_idx"], Kd, Nd)
+        torch.cuda.synchronize()
+        sched_info = dict(schedule.info(), build_wall_ms=(time.perf_counter() - t0) * 1e3)
+        if schedule.active:
+            chosen, launches_per_step = "scheduled", 4
+        else:
+            schedule = None
 
     # ---- timed region -------------------------------------------------------------------------------
     def barrier():
@@ -443,28 +520,20 @@ def main(argv=None):
     barrier()
     with ClockSampler(physical_gpu_index(local)) as clocks:
         barrier()
-        sec = time_spmm(torch, ops, t, C_out, workspace, ns.kernel, ns.steps, ns.warmup, flush_buf)
+        sec = time_spmm(torch, ops, t, C_out, None if schedule is not None else workspace, ns.kernel, ns.steps, ns.warmup,
+                        flush_buf, schedule=schedule)
         barrier()
     sec_max = D.max_over_ranks(sec, dev)
     flops_total = 2.0 * nnz * Nd
     value = flops_total / sec_max / 1e9
 
-    # sanity: a sample of this rank's rows against the CPU oracle (outside every timed region)
+    # parity on a row sample against the CPU oracle (outside every timed region): strict elementwise pass
+    # rate at rtol 1e-5 / atol 1e-6 against the sequential fp32 oracle, and the worst error in units of the
+    # accumulation-order bound 1e-5 * sum|a*b| + 1e-6 against the fp64 oracle (must be <= 1)
     check = None
     if rank == 0 and not ns.no_extras and not ns.only_e2e:
         import oracle
-        rows = np.unique(np.concatenate([np.random.default_rng(0).integers(0, my_rows, 512),
-                                         np.argsort(np.diff(shard.row_ptr.cpu().numpy()))[-4:]]))
-        rp_l = shard.row_ptr.cpu().numpy().astype(np.int64)
-        idx = np.concatenate([np.arange(rp_l[r], rp_l[r + 1]) for r in rows])
-        idx_d = torch.from_numpy(idx).to(dev)
-        uniq, inv = torch.unique(t["col_idx"][idx_d].long(), return_inverse=True)
-        sub_rp = np.zeros(len(rows) + 1, np.int32)
-        np.cumsum(rp_l[rows + 1] - rp_l[rows], out=sub_rp[1:])
-        f64, mag = oracle.spmm_f64(sub_rp, inv.to(torch.int32).cpu().numpy(), t["values"][idx_d].cpu().numpy(),
-                                   B[uniq].cpu().numpy(), threads=oracle.max_threads())
-        got = C_out[torch.from_numpy(rows).to(dev)].cpu().numpy()
-        check = bool((np.abs(got - f64) <= 1e-5 * mag + 1e-6).all())
+        check = tolerance_report(torch, oracle, shard.row_ptr, t["col_idx"], t["values"], B, C_out)
 
     # ---- end to end: pinned host buffers in, host C out ---------------------------------------------
     # N = 1: csrspmm_b200_spmm_host (one C-ABI call does the copies and the product).
@@ -485,14 +554,20 @@ def main(argv=None):
                 os.environ["CSRSPMM_HOST_PANELS"] = str(ns.e2e_panels)
             n_panels = len(D.column_panels(Kd, Nd, ns.e2e_panels or None))
 
-            def e2e_step():
+            def e2e_step():  # the matrix stays on the device between products; B goes up and C comes back every step
+                ops.spmm_host(t["row_ptr"], t["col_idx"], t["values"], h["B"], C_host, 1.0, 0.0, kernel=ns.kernel,
+                              arena=arena, device=dev)
+
+            def e2e_step_with_a():  # everything from the host, A included
                 ops.spmm_host(h["row_ptr"], h["col_idx"], h["values"], h["B"], C_host, 1.0, 0.0, kernel=ns.kernel,
                               arena=arena, device=dev)
 
-            h2d = my_nnz * 8 + (my_rows + 1) * 4 + Kd * Nd * 4
+            h2d = Kd * Nd * 4
+            h2d_with_a = my_nnz * 8 + (my_rows + 1) * 4 + Kd * Nd * 4
             d2h, xchg = my_rows * Nd * 4, 0
-            api = (f"csrspmm_b200_spmm_host (pinned host A, B in, host C out; {n_panels} column panel(s): uploads, "
-                   "kernels and downloads of different panels overlap)")
+            api = (f"csrspmm_b200_spmm_host (per step: pinned host B in, host C out; A resident on the device, as over "
+                   f"repeated products on one matrix; {n_panels} column panel(s): uploads, kernels and downloads of "
+                   "different panels overlap)")
         else:
             sl = Kd // world
             hs = D.Shard(rank, world, shard.row_lo, shard.row_hi,
@@ -501,12 +576,15 @@ def main(argv=None):
             hB = B[rank * sl:(rank + 1) * sl].cpu().pin_memory()
             del t, B, shard, C_out, workspace
             torch.cuda.empty_cache()
-            runner = D.ShardedHostSpmm(hs, hB, Kd, dev, kernel=ns.kernel, panels=ns.e2e_panels or None)
+            runner = D.ShardedHostSpmm(hs, hB, Kd, dev, kernel=ns.kernel, panels=ns.e2e_panels or None, keep_matrix=True)
             e2e_step = runner.run
+            e2e_step_with_a = None
             n_panels = len(runner.panels)
             h2d, d2h, xchg = runner.h2d_bytes, runner.d2h_bytes, runner.exchange_bytes
-            api = ("distributed.ShardedHostSpmm (per rank: pinned host block of A and 1/N of B in, NCCL all-gather of "
-                   f"B, host block of C out; {n_panels} column panel(s), the stages of different panels overlap)")
+            h2d_with_a = h2d + hs.nnz * 8 + (hs.rows + 1) * 4
+            api = ("distributed.ShardedHostSpmm (per rank and step: pinned host 1/N of B in, NCCL all-gather of B, host "
+                   f"block of C out; the rank's block of A resident on the device; {n_panels} column panel(s), the stages "
+                   "of different panels overlap)")
         torch.cuda.synchronize()
         e2e_step()  # warm-up
         # every call is synchronous (it returns when C is in host memory), so each is timed by itself, as
@@ -527,6 +605,29 @@ def main(argv=None):
                "d2h_bytes_per_step": int(d2h), "nvlink_bytes_per_step": int(xchg), "ms_per_step": e2e_sec * 1e3,
                "ms_min": min(per_call) * 1e3, "ms_max": max(per_call) * 1e3,
                "steps": ns.e2e_steps, "bytes_are": "per rank", "column_panels": n_panels, "api": api}
+        if e2e_step_with_a is not None:  # the same call with A uploaded every step as well
+            e2e_step_with_a()
+            with_a = []
+            for _ in range(2):
+                t0 = time.perf_counter()
+                e2e_step_with_a()
+                torch.cuda.synchronize()
+                with_a.append(time.perf_counter() - t0)
+            e2e["with_A_uploaded_every_step"] = {"ms_per_step": min(with_a) * 1e3, "h2d_bytes_per_step": int(h2d_with_a)}
+        # what the host link gives with nothing but copies on it, all ranks at once: the floor of a step is the
+        # larger of (bytes up / rate up) and (bytes down / rate down) when both directions run together
+        if not ns.no_copy_ceiling:
+            if world > 1:
+                del runner
+            else:
+                del arena
+            torch.cuda.empty_cache()
+            cc = copy_ceiling(torch, dev, barrier, D)
+            rate = cc["GBps_per_rank_each_way_together"] * 1e9
+            cc["floor_ms_per_step"] = max(h2d, d2h) / rate * 1e3
+            cc["e2e_over_floor"] = e2e_sec * 1e3 / cc["floor_ms_per_step"]
+            cc["aggregate_GBps_each_way"] = cc["GBps_per_rank_each_way_together"] * world
+            e2e["copy_ceiling"] = cc
 
     if world > 1:
         barrier()
@@ -537,6 +638,7 @@ def main(argv=None):
         return 0
 
     peak, peak_kind = measured_peak()
+    traffic = ncu_traffic(prob.name, chosen, my_nnz)
     achieved = my_bytes / sec / 1e9
     gather_bytes = my_nnz * Nd * 4.0
     line = {
@@ -551,15 +653,18 @@ def main(argv=None):
                    "broadcast_s": round(t_bcast, 3)},
         "gpu_launches": ns.steps * launches_per_step,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "traffic": ncu_traffic(prob.name, chosen, my_nnz), "peak_kind": f"of {peak_kind}",
+                     "traffic": (traffic or {}).get("bytes"), "traffic_source": traffic, "peak_kind": f"of {peak_kind}",
                      "algorithmic_bytes": my_bytes, "b_rows_touched": touched,
                      "gather_bytes": gather_bytes, "gather_GBps": gather_bytes / sec / 1e9,
                      "gather_frac": gather_bytes / sec / 1e9 / peak,
-                     "scope": "rank 0's row block, main kernel + fix-up kernel"},
+                     "scope": "rank 0's row block, every kernel of a step"},
         "clocks": clocks.summary(),
     }
     if check is not None:
-        line["oracle_check"] = check
+        line["oracle_check"] = check["within_bound"]
+        line["parity"] = check
+    if sched_info is not None:
+        line["schedule"] = sched_info
     if e2e is not None:
         line["e2e"] = e2e
 
@@ -570,8 +675,16 @@ def main(argv=None):
         line["cpu_baseline"] = {"value": g, "unit": "GFLOPS", "cores": oracle.max_threads(), "kind": "port",
                                 "sample": f"rows [0, {rows}) of {M} ({n_s} of {nnz} nnz), B complete on the host, "
                                           f"best of 3 passes, {best:.2f} s per pass"}
+        if schedule is not None:  # the same product without the schedule (the plain AUTO kernel), for comparison
+            plain = ops.selected_kernel(my_rows, Kd, Nd, my_nnz, kernel=ns.kernel, max_row_nnz=0)
+            sec_plain = time_spmm(torch, ops, t, C_out, workspace, ns.kernel, min(ns.steps, 5), 3, flush_buf)
+            line["without_schedule"] = {"kernel": plain, "ms_per_step": sec_plain * 1e3, "gflops": flops_total / sec_plain / 1e9,
+                                        "roofline_frac": my_bytes / sec_plain / 1e9 / peak,
+                                        "traffic": (ncu_traffic(prob.name, plain, my_nnz) or {}).get("bytes")}
         line["cusparse"] = cusparse_summary(
             cusparse_direct(torch, t, my_rows, Kd, Nd, my_nnz, C_out, min(ns.steps, 5), 2, flush_buf), flops_total)
+        if isinstance(line["cusparse"], dict) and "us" in line["cusparse"]:
+            line["speedup_over_cusparse_best"] = line["cusparse"]["us"] / (sec * 1e6)
         del prob, t, B, C_out, workspace, shard
         torch.cuda.empty_cache()
         line["other_workloads"] = other_workloads(torch, ops, G, ns, dev, peak)
@@ -583,7 +696,9 @@ def main(argv=None):
 
 
 def other_workloads(torch, ops, G, ns, dev, peak):
-    """Kernel-only numbers for the other BASELINE configs (1 GPU), each next to cuSPARSE."""
+    """Kernel-only numbers for the other BASELINE configs (1 GPU), each next to cuSPARSE, with the parity
+    figures of every kernel on a row sample."""
+    import oracle
     out = {}
     for name in ("cfg1_check", "cfg2_medium", "cfg3_powerlaw", "cfg4_fp4"):
         if name == ns.workload:
@@ -598,26 +713,58 @@ def other_workloads(torch, ops, G, ns, dev, peak):
             mx = ops.row_stats(p.row_ptr)["max_row_nnz"]
             nbytes, _ = problem_bytes(G, t, p.M, p.Nd, p.nnz, p.Kd)
             flops = 2.0 * p.nnz * p.Nd
-            entry = {"nnz": p.nnz, "max_row_nnz": mx, "l2_flushed": fb is not None, "kernels": {}}
+            gather = p.nnz * p.Nd * 4.0
+            entry = {"nnz": p.nnz, "max_row_nnz": mx, "l2_flushed": fb is not None, "algorithmic_bytes": nbytes,
+                     "gather_bytes": gather, "kernels": {}}
             for k in ("row", "merge", "tma"):
                 sec = time_spmm(torch, ops, t, C_out, ws, k, 20, 3, fb, max_row_nnz=mx)
                 entry["kernels"][k] = {"gflops": flops / sec / 1e9, "us": sec * 1e6,
-                                       "roofline_frac": nbytes / sec / 1e9 / peak}
+                                       "roofline_frac": nbytes / sec / 1e9 / peak,
+                                       "parity": tolerance_report(torch, oracle, p.row_ptr, p.col_idx, p.values, p.B, C_out)}
             auto = ops.selected_kernel(p.M, p.Kd, p.Nd, p.nnz, max_row_nnz=mx)
             entry["auto"] = auto
+            sec_auto = entry["kernels"][auto]["us"] / 1e6
+            tr = ncu_traffic(name, auto, p.nnz)
+            entry["roofline"] = {"bound": "hbm" if name == "cfg3_powerlaw" else "l2", "kernel": auto,
+                                 "achieved_GBps": nbytes / sec_auto / 1e9, "frac_of_measured_hbm_peak": nbytes / sec_auto / 1e9 / peak,
+                                 "gather_TBps_l2_to_sm": gather / sec_auto / 1e12,
+                                 "fp32_fma_TFLOPS": flops / sec_auto / 1e12,
+                                 "frac_of_fp32_fma_peak": flops / sec_auto / 1e12 / FP32_FMA_PEAK_TFLOPS,
+                                 "traffic": tr}
+            # a schedule at the library's own choice (inactive for narrow rows of B), and for config 3 one with
+            # a threshold given, to show what it costs there
+            sch = ops.Schedule(p.row_ptr, p.col_idx, p.Kd, p.Nd)
+            entry["schedule_auto"] = sch.info()
+            if name == "cfg3_powerlaw":
+                forced = ops.Schedule(p.row_ptr, p.col_idx, p.Kd, p.Nd, threshold=64, slab_rows=(32 << 20) // (p.Nd * 4))
+                sec = time_spmm(torch, ops, t, C_out, None, "auto", 20, 3, fb, schedule=forced)
+                entry["kernels"]["scheduled_threshold_64"] = {
+                    "gflops": flops / sec / 1e9, "us": sec * 1e6, "roofline_frac": nbytes / sec / 1e9 / peak,
+                    "schedule": forced.info(),
+                    "parity": tolerance_report(torch, oracle, p.row_ptr, p.col_idx, p.values, p.B, C_out)}
+                del forced
+            del sch
             if fb is not None and p.nnz < 1_000_000:  # launch-bound sizes: how the call is issued matters
-                entry["launch_modes_auto_kernel"] = launch_bound_modes(torch, ops, t, C_out, ws, auto, mx, fb)
+                modes = launch_bound_modes(torch, ops, t, C_out, ws, auto, mx, fb)
+                for key in ("cold_us_median", "warm_us", "graph_us"):  # the same roofline, per way of launching
+                    modes[key.replace("_us", "").replace("_median", "") + "_roofline_frac"] = nbytes / (modes[key] * 1e-6) / 1e9 / peak
+                entry["launch_modes_auto_kernel"] = modes
             cs = cusparse_via_torch(torch, t, p.M, p.Kd, 20, 3, fb)
             entry["cusparse_torch"] = {"gflops": flops / cs / 1e9, "us": cs * 1e6} if isinstance(cs, float) else cs
             entry["cusparse"] = cusparse_summary(cusparse_direct(torch, t, p.M, p.Kd, p.Nd, p.nnz, C_out, 20, 3, fb), flops)
+            if isinstance(entry["cusparse"], dict) and "us" in entry["cusparse"]:
+                entry["speedup_over_cusparse_best"] = entry["cusparse"]["us"] / (sec_auto * 1e6)
             if name == "cfg4_fp4":
                 packed, scale = ops.e2m1_quantize(p.values)
                 e = (packed.to(dev), scale, p.nnz)
+                decoded = ops.e2m1_dequantize(e[0], p.nnz, scale)
                 nb4, _ = problem_bytes(G, t, p.M, p.Nd, p.nnz, p.Kd, 0.5)
                 for k in ("row", "merge", "tma"):
                     sec = time_spmm(torch, ops, t, C_out, ws, k, 20, 3, fb, max_row_nnz=mx, e2m1=e)
                     entry["kernels"][k + "_e2m1"] = {"gflops": flops / sec / 1e9, "us": sec * 1e6,
-                                                     "roofline_frac": nb4 / sec / 1e9 / peak}
+                                                     "roofline_frac": nb4 / sec / 1e9 / peak,
+                                                     "parity_on_decoded_values": tolerance_report(
+                                                         torch, oracle, p.row_ptr, p.col_idx, decoded, p.B, C_out)}
             out[name] = entry
             del p, t, C_out, ws, fb
             torch.cuda.empty_cache()

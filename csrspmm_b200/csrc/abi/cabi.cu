@@ -217,6 +217,18 @@ int enqueue(const csrspmm_b200_args* a, cudaStream_t st)
 
 size_t align256(size_t v) { return (v + 255) / 256 * 256; }
 
+// True when `ptr` is device memory of the current context (an operand the caller kept on the GPU).
+bool on_device(const void* ptr)
+{
+    if (ptr == nullptr) return false;
+    cudaPointerAttributes attr;
+    if (cudaPointerGetAttributes(&attr, ptr) != cudaSuccess) {
+        cudaGetLastError();  // plain host memory on older drivers: not an error for us
+        return false;
+    }
+    return attr.type == cudaMemoryTypeDevice;
+}
+
 // ---- host round trip in column panels -------------------------------------------------------
 //
 // C[:, panel] depends on B[:, panel] only, so a wide product whose operands start in host memory
@@ -473,14 +485,21 @@ int csrspmm_b200_spmm_host(const csrspmm_b200_args* a, void* device_arena, size_
     void* d_ws = cur; cur += align256(ws_bytes);
     int32_t* d_status = reinterpret_cast<int32_t*>(cur);
 
+    // A may already be on the device (kept there by the caller between products on one matrix, where
+    // only B changes): each of its three arrays that is device memory is used in place, not copied.
+    const bool rp_dev = on_device(a->row_ptr), ci_dev = on_device(a->col_idx), va_dev = on_device(a->values);
+    if (rp_dev) d_rp = const_cast<int32_t*>(a->row_ptr);
+    if (ci_dev) d_ci = const_cast<int32_t*>(a->col_idx);
+    if (va_dev) d_va = const_cast<char*>(static_cast<const char*>(a->values));
+
     const int panels = column_panel_layout(a->Kd, a->Nd, 0, nullptr, nullptr);
     if (panels > 1) {
         // A first, on the caller's stream; the panels of B follow it on the same stream
         int word = 0;
         cudaError_t e = cudaMemsetAsync(d_status, 0, 4, st);
-        if (e == cudaSuccess) e = cudaMemcpyAsync(d_rp, a->row_ptr, rp_bytes, cudaMemcpyHostToDevice, st);
-        if (e == cudaSuccess && a->nnz > 0) e = cudaMemcpyAsync(d_ci, a->col_idx, ci_bytes, cudaMemcpyHostToDevice, st);
-        if (e == cudaSuccess && a->nnz > 0) e = cudaMemcpyAsync(d_va, a->values, vbytes, cudaMemcpyHostToDevice, st);
+        if (e == cudaSuccess && !rp_dev) e = cudaMemcpyAsync(d_rp, a->row_ptr, rp_bytes, cudaMemcpyHostToDevice, st);
+        if (e == cudaSuccess && a->nnz > 0 && !ci_dev) e = cudaMemcpyAsync(d_ci, a->col_idx, ci_bytes, cudaMemcpyHostToDevice, st);
+        if (e == cudaSuccess && a->nnz > 0 && !va_dev) e = cudaMemcpyAsync(d_va, a->values, vbytes, cudaMemcpyHostToDevice, st);
         if (e != cudaSuccess) {
             set_last_error("spmm_host: upload of A failed: %s", cudaGetErrorString(e));
             status = CSRSPMM_B200_ERR_CUDA;
@@ -510,10 +529,21 @@ int csrspmm_b200_spmm_host(const csrspmm_b200_args* a, void* device_arena, size_
     int blocks = (c_bytes >= ((size_t)64 << 20) && a->M >= 64) ? kMaxBlocks : 1;
     int32_t bounds[kMaxBlocks + 1] = {0};
     bounds[1] = a->M;
-    if (blocks > 1 && csrspmm_b200_partition_rows(a->M, a->row_ptr, blocks, 1.0, bounds) != CSRSPMM_B200_OK) blocks = 1;
+    // the row blocks are cut on the host: a row_ptr that lives on the device is read back once (4 bytes per row)
+    const int32_t* h_rp = a->row_ptr;
+    int32_t* h_rp_copy = nullptr;
+    if (blocks > 1 && rp_dev) {
+        h_rp_copy = static_cast<int32_t*>(std::malloc(rp_bytes));
+        if (h_rp_copy == nullptr || cudaMemcpy(h_rp_copy, a->row_ptr, rp_bytes, cudaMemcpyDeviceToHost) != cudaSuccess) {
+            cudaGetLastError();
+            blocks = 1;
+        }
+        h_rp = h_rp_copy;
+    }
+    if (blocks > 1 && csrspmm_b200_partition_rows(a->M, h_rp, blocks, 1.0, bounds) != CSRSPMM_B200_OK) blocks = 1;
     if (blocks > 1 && e2m1)  // packed values can only be offset by whole bytes
         for (int k = 1; k < blocks; ++k)
-            if (a->row_ptr[bounds[k]] & 1) blocks = 1;
+            if (h_rp[bounds[k]] & 1) blocks = 1;
     if (blocks == 1) bounds[1] = a->M;
 
     cudaStream_t copy_stream = nullptr;
@@ -524,6 +554,8 @@ int csrspmm_b200_spmm_host(const csrspmm_b200_args* a, void* device_arena, size_
         // arena, or into this frame's `word`, when they go away (errors of these waits are ignored)
         cudaStreamSynchronize(st);
         if (copy_stream) cudaStreamSynchronize(copy_stream);
+        std::free(h_rp_copy);
+        h_rp_copy = nullptr;
         for (int k = 0; k < events; ++k) cudaEventDestroy(done[k]);
         if (copy_stream) cudaStreamDestroy(copy_stream);
         if (owned) cudaFreeAsync(arena, st);
@@ -543,10 +575,10 @@ int csrspmm_b200_spmm_host(const csrspmm_b200_args* a, void* device_arena, size_
         for (; events < blocks; ++events) CUDA_TRY_HOST(cudaEventCreateWithFlags(&done[events], cudaEventDisableTiming));
     }
     CUDA_TRY_HOST(cudaMemsetAsync(d_status, 0, 4, st));
-    CUDA_TRY_HOST(cudaMemcpyAsync(d_rp, a->row_ptr, rp_bytes, cudaMemcpyHostToDevice, st));
+    if (!rp_dev) CUDA_TRY_HOST(cudaMemcpyAsync(d_rp, a->row_ptr, rp_bytes, cudaMemcpyHostToDevice, st));
     if (a->nnz > 0) {
-        CUDA_TRY_HOST(cudaMemcpyAsync(d_ci, a->col_idx, ci_bytes, cudaMemcpyHostToDevice, st));
-        CUDA_TRY_HOST(cudaMemcpyAsync(d_va, a->values, vbytes, cudaMemcpyHostToDevice, st));
+        if (!ci_dev) CUDA_TRY_HOST(cudaMemcpyAsync(d_ci, a->col_idx, ci_bytes, cudaMemcpyHostToDevice, st));
+        if (!va_dev) CUDA_TRY_HOST(cudaMemcpyAsync(d_va, a->values, vbytes, cudaMemcpyHostToDevice, st));
     }
     if (a->Kd > 0) {
         // B rows are packed on the device (ldb = Nd) whatever the host stride is
@@ -560,7 +592,8 @@ int csrspmm_b200_spmm_host(const csrspmm_b200_args* a, void* device_arena, size_
     for (int k = 0; k < blocks; ++k) {
         const int32_t r0 = bounds[k], r1 = bounds[k + 1];
         if (r1 <= r0) continue;
-        const int32_t j0 = a->row_ptr[r0], j1 = a->row_ptr[r1];
+        // (one block: the whole matrix, and row_ptr may be device memory that the host cannot read)
+        const int32_t j0 = blocks > 1 ? h_rp[r0] : 0, j1 = blocks > 1 ? h_rp[r1] : (int32_t)a->nnz;
         csrspmm_b200_args d = *a;
         d.M = r1 - r0;
         d.nnz = (int64_t)j1 - j0;

@@ -128,10 +128,13 @@ class ShardedHostSpmm:
     PCIe and panel q-1 of C is already leaving -- uploads, NVLink exchange, kernels and downloads of
     different panels run at the same time, each stage on its own stream.  On the device each panel of B and
     of C is stored contiguously; every element of C is the same sum as in the unsplit product.
+
+    ``keep_matrix=True`` uploads the block of A once, here, and keeps it on the device: ``run()`` then moves
+    only B and C (repeated products on one matrix, where only B changes).
     """
 
     def __init__(self, shard_host: "Shard", B_slice_host: torch.Tensor, Kd: int, device, kernel: str = "auto",
-                 panels: int | None = None):
+                 panels: int | None = None, keep_matrix: bool = False):
         import torch.distributed as dist
         from . import ops
         self.dist, self.ops, self.dev = dist, ops, torch.device(device)
@@ -163,17 +166,24 @@ class ShardedHostSpmm:
             self.ev_up = [torch.cuda.Event() for _ in self.panels]
             self.ev_gather = [torch.cuda.Event() for _ in self.panels]
             self.ev_mul = [torch.cuda.Event() for _ in self.panels]
-        self.h2d_bytes = (rows + 1) * 4 + shard_host.nnz * 8 + self.slice_rows * Nd * 4
+        self.keep_matrix = bool(keep_matrix)
+        if self.keep_matrix:
+            self.d_rp.copy_(self.h_rp)
+            self.d_ci.copy_(self.h_ci)
+            self.d_va.copy_(self.h_va)
+            torch.cuda.synchronize(d)
+        self.h2d_bytes = (0 if self.keep_matrix else (rows + 1) * 4 + shard_host.nnz * 8) + self.slice_rows * Nd * 4
         self.d2h_bytes = rows * Nd * 4
         self.exchange_bytes = (Kd - self.slice_rows) * Nd * 4  # received over NVLink per rank
 
     def run(self) -> torch.Tensor:
         k0, k1 = self.rank * self.slice_rows, (self.rank + 1) * self.slice_rows
         self.s_up.wait_stream(torch.cuda.current_stream(self.dev))
-        with torch.cuda.stream(self.s_up):
-            self.d_rp.copy_(self.h_rp, non_blocking=True)
-            self.d_ci.copy_(self.h_ci, non_blocking=True)
-            self.d_va.copy_(self.h_va, non_blocking=True)
+        if not self.keep_matrix:
+            with torch.cuda.stream(self.s_up):
+                self.d_rp.copy_(self.h_rp, non_blocking=True)
+                self.d_ci.copy_(self.h_ci, non_blocking=True)
+                self.d_va.copy_(self.h_va, non_blocking=True)
         for q, (c0, w) in enumerate(self.panels):
             mine = self.d_B[q][k0:k1]
             with torch.cuda.stream(self.s_up):

@@ -401,7 +401,9 @@ def row_stats(row_ptr) -> dict:
 def spmm_host(row_ptr, col_idx, values, B, C_host, alpha=1.0, beta=0.0, *, entry="naive", kernel="auto",
               max_row_nnz=0, arena=None, device=None):
     """End-to-end call on HOST tensors (ideally pinned): copies A and B in, multiplies, copies C
-    back into C_host and waits.  ``arena`` is an optional CUDA uint8 tensor to stage in."""
+    back into C_host and waits.  ``arena`` is an optional CUDA uint8 tensor to stage in.  row_ptr, col_idx
+    and values may be CUDA tensors instead (a matrix kept on the GPU between products): they are then used
+    in place and only B goes up."""
     M = row_ptr.numel() - 1
     Kd, Nd = B.shape
     a = _lib.make_args(M, Kd, Nd, col_idx.numel(), row_ptr.data_ptr(), col_idx.data_ptr(), values.data_ptr(),

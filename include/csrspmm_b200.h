@@ -130,6 +130,8 @@ int csrspmm_b200_spmm_sync(const csrspmm_b200_args* args, csrspmm_b200_stream_t 
  * beta != 0) to the current device, runs the SpMM, copies C back and waits.  When
  * device_arena is NULL the device buffers are allocated and released inside the call; else
  * the arena (>= csrspmm_b200_host_arena_bytes(args) bytes, 256-byte aligned) is used.
+ * row_ptr, col_idx and values may each be DEVICE memory instead (a matrix the caller keeps on the GPU
+ * between products, where only B changes): such an array is used in place and not copied.
  * Copies and kernels overlap: a B of 256 MiB or more with Nd >= 256 is processed in column panels
  * of 128 columns (panel q+1 of B arrives and panel q-1 of C leaves while panel q is multiplied;
  * CSRSPMM_HOST_PANELS=<n> in the environment sets the number of panels, 1 = none); otherwise a

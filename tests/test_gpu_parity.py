@@ -500,6 +500,33 @@ def test_host_round_trip_in_row_blocks(cuda_lib):
     assert (np.abs(C_host.numpy() - f64b) <= RTOL * magb + ATOL).all()
 
 
+@pytest.mark.parametrize("panels", [1, 3])
+def test_host_round_trip_with_the_matrix_kept_on_the_device(cuda_lib, monkeypatch, panels):
+    """csrspmm_b200_spmm_host with row_ptr / col_idx / values already on the GPU (a matrix reused over many
+    products, only B changes): used in place, same result as with every operand on the host -- in one piece,
+    in row blocks (whose cuts need row_ptr on the host: read back once) and in column panels."""
+    p = G.make("cfg3_powerlaw", scale=8, Nd=192)
+    assert p.M * p.Nd * 4 >= 64 << 20  # large enough for row blocks when there are no panels
+    monkeypatch.setenv("CSRSPMM_HOST_PANELS", str(panels))
+    h = [torch.from_numpy(x).pin_memory() for x in arrays(p)]
+    d = [x.cuda() for x in h[:3]]
+    all_host = torch.empty(p.M, p.Nd).pin_memory()
+    ops.spmm_host(*h, all_host)
+    kept = torch.empty(p.M, p.Nd).pin_memory()
+    ops.spmm_host(*d, h[3], kept)
+    assert torch.equal(kept, all_host)
+    mixed = torch.empty(p.M, p.Nd).pin_memory()
+    ops.spmm_host(d[0], h[1], d[2], h[3], mixed)  # any subset may be resident
+    assert torch.equal(mixed, all_host)
+    f64, mag = oracle.spmm_f64(p.row_ptr, p.col_idx, p.values, p.B, threads=4)
+    assert (np.abs(kept.numpy() - f64) <= RTOL * mag + ATOL).all()
+    small = G.random_csr(300, 200, 24, 0.05, seed=12)  # one block, no panels
+    hs = [torch.from_numpy(x) for x in arrays(small)]
+    out = torch.empty(small.M, small.Nd)
+    ops.spmm_host(*(x.cuda() for x in hs[:3]), hs[3], out, max_row_nnz=int(np.diff(small.row_ptr).max()))
+    assert np.array_equal(out.numpy(), oracle.spmm(*arrays(small), threads=4))
+
+
 def test_randomised_shapes_all_kernels(cuda_lib):
     """Forty seeded random problems: odd sizes, empty and very long rows, unsorted and repeated
     column indices (the kernels, like the reference's, take stored order as it comes)."""
