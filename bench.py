@@ -424,6 +424,9 @@ def main(argv=None):
     ap.add_argument("--kernel", default="auto", choices=["auto", "row", "merge", "tma"])
     ap.add_argument("--no-extras", action="store_true", help="skip e2e, cpu_baseline and other_workloads")
     ap.add_argument("--no-schedule", action="store_true", help="never build a per-matrix schedule (plain AUTO kernel)")
+    ap.add_argument("--sched-threshold", type=int, default=0, help="rows of this many entries or more are scheduled (0: the library's choice)")
+    ap.add_argument("--sched-slab-mib", type=int, default=0, help="MiB of B per slab of a schedule (0: the library's choice)")
+    ap.add_argument("--sched-piece", type=int, default=0, help="longest piece of a scheduled row (0: the library's choice)")
     ap.add_argument("--only-e2e", action="store_true",
                     help="keep e2e but skip the oracle check, cpu_baseline, cuSPARSE and other_workloads")
     ap.add_argument("--e2e-steps", type=int, default=5)
@@ -503,7 +506,8 @@ def main(argv=None):
     if ns.kernel == "auto" and not ns.no_schedule and my_rows > 0:
         torch.cuda.synchronize()
         t0 = time.perf_counter()
-        schedule = ops.Schedule(t["row_ptr"], t["col_idx"], Kd, Nd)
+        schedule = ops.Schedule(t["row_ptr"], t["col_idx"], Kd, Nd, threshold=ns.sched_threshold,
+                                slab_rows=(ns.sched_slab_mib << 20) // (Nd * 4), piece_nnz=ns.sched_piece)
         torch.cuda.synchronize()
         sched_info = dict(schedule.info(), build_wall_ms=(time.perf_counter() - t0) * 1e3)
         if schedule.active:
