@@ -103,7 +103,7 @@ cudaError_t launch_tma(const SpmmParams& p, const Plan& plan, cudaStream_t st)
     // instantiation, for the largest ring the kernel can ask for (rows of 2 KB), so that later
     // calls -- inside a stream capture too -- are a plain launch.  Racing first calls repeat the
     // same setting.
-    constexpr int kMaxRing = 8 * (CSRSPMM_TUNE_TMA_SLOTS * 2048 > 512 * NV ? CSRSPMM_TUNE_TMA_SLOTS * 2048 : 512 * NV);
+    constexpr int kMaxRing = (CSRSPMM_TUNE_MERGE_THREADS / 32) * (CSRSPMM_TUNE_TMA_SLOTS * 2048 > 512 * NV ? CSRSPMM_TUNE_TMA_SLOTS * 2048 : 512 * NV);
     static bool configured[64] = {};
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
@@ -115,7 +115,7 @@ cudaError_t launch_tma(const SpmmParams& p, const Plan& plan, cudaStream_t st)
         if (dev >= 0 && dev < 64) configured[dev] = true;
     }
     kern<<<(unsigned)plan.grid, kMergeThreads, plan.dynamic_smem, st>>>(p, (unsigned)plan.tma_slot_bytes,
-                                                                        (unsigned)(plan.dynamic_smem / 8));
+                                                                        (unsigned)(plan.dynamic_smem / (CSRSPMM_TUNE_MERGE_THREADS / 32)));
     return cudaSuccess;
 }
 

@@ -117,7 +117,7 @@ static int forced_kernel_from_env()
 
 int merge_tile_for(int shape, long long num_items, bool* small)
 {
-    const int groups = 256 / kShapes[shape].G;
+    const int groups = CSRSPMM_TUNE_MERGE_THREADS / kShapes[shape].G;
     const int big = groups * kShapes[shape].TG;
     const bool use_small = CSRSPMM_TUNE_MERGE_TG_SMALL < kShapes[shape].TG &&
                            num_items < (long long)big * 148 * CSRSPMM_TUNE_MERGE_SMALL_BELOW_CTAS_PER_SM;
@@ -185,12 +185,12 @@ int make_plan(const csrspmm_b200_args* a, Plan* plan)
         plan->G = 32;
         plan->NV = plan->ncolv <= 32 ? 1 : (plan->ncolv <= 64 ? 2 : 4);
         plan->shape = plan->NV == 1 ? 2 : (plan->NV == 2 ? 3 : 4);
-        fill_split_geometry(a, plan, 8 * CSRSPMM_TUNE_TMA_TG);
+        fill_split_geometry(a, plan, (CSRSPMM_TUNE_MERGE_THREADS / 32) * CSRSPMM_TUNE_TMA_TG);
         const size_t slot = align_up((size_t)a->Nd * 4, 128);
         size_t ring = (size_t)CSRSPMM_TUNE_TMA_SLOTS * slot;          // per warp
         if (ring < (size_t)512 * plan->NV) ring = (size_t)512 * plan->NV;  // must also hold the partial sums
         plan->tma_slot_bytes = slot;
-        plan->dynamic_smem = 8 /*warps*/ * ring;
+        plan->dynamic_smem = (CSRSPMM_TUNE_MERGE_THREADS / 32) /*warps*/ * ring;
     } else {
         plan->shape = shape_for(plan->ncolv);
         plan->G = kShapes[plan->shape].G;
@@ -225,7 +225,7 @@ size_t worst_case_workspace(const csrspmm_b200_args* a, bool any_row_block)
     // a large matrix may fall under the small-problem threshold although the whole matrix does not,
     // so a caller that multiplies row blocks out of one scratch buffer asks for the small tile
     // whatever the size (any_row_block).
-    int tile = 8 * CSRSPMM_TUNE_TMA_TG;  // TMA kernel
+    int tile = (CSRSPMM_TUNE_MERGE_THREADS / 32) * CSRSPMM_TUNE_TMA_TG;  // TMA kernel
     for (int k = 0; k < kNumShapes; ++k) {
         const int t = merge_tile_for(k, any_row_block ? 0 : (long long)a->M + a->nnz, nullptr);
         if (t < tile) tile = t;

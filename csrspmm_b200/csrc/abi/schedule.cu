@@ -176,7 +176,7 @@ int scheduled_plan(const csrspmm_b200_args* a, Plan* plan)
     if (status != CSRSPMM_B200_OK) return status;
     if (plan->small_tile) {  // few items but a large B: keep the one instantiated tile
         plan->small_tile = false;
-        const int tile = (256 / kShapes[plan->shape].G) * kShapes[plan->shape].TG;
+        const int tile = (CSRSPMM_TUNE_MERGE_THREADS / kShapes[plan->shape].G) * kShapes[plan->shape].TG;
         plan->tile = tile;
         plan->num_tiles = (plan->num_items + tile - 1) / tile;
         plan->grid = plan->num_tiles;

@@ -32,7 +32,7 @@
 
 namespace csrspmm_b200 {
 
-constexpr int kMergeThreads = 256;
+constexpr int kMergeThreads = CSRSPMM_TUNE_MERGE_THREADS;
 
 // First i in [max(0, d-nnz), min(d, M)] with row_end[i] > d - i - 1; then j = d - i positions
 // precede the diagonal.  Cooperative over one full warp: 32 probes per round.

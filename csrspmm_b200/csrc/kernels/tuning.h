@@ -83,6 +83,11 @@
 #define CSRSPMM_TUNE_P4_D 4
 #endif
 
+// threads per CTA of the merge-path kernels (merge, bulk-copy): lane groups per CTA = this / G
+#ifndef CSRSPMM_TUNE_MERGE_THREADS
+#define CSRSPMM_TUNE_MERGE_THREADS 256
+#endif
+
 // L2 residency hints: rows of B loaded with an evict_last policy applied to this percentage of
 // the lines, C written with streaming stores.  Both are OFF by default: on B200 neither helped
 // (config 3, B = 2.1 x L2: 685 us without hints, 687-714 us with any combination of them).
