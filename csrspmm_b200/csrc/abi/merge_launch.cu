@@ -28,9 +28,26 @@ void launch_merge(const SpmmParams& p, const Plan& plan, cudaStream_t st)
     }
 }
 
+// very narrow dense operands: lane groups of 1, 2 or 4 lanes (kNarrowShapes)
+template <int K, int VW, int FMT>
+void launch_merge_narrow(const SpmmParams& p, const Plan& plan, cudaStream_t st)
+{
+    constexpr int G = kNarrowShapes[K].G, NV = kNarrowShapes[K].NV, TG = kNarrowShapes[K].TG;
+    constexpr int U = VW == 1 ? 8 : merge_unroll(NV);
+    const unsigned grid = (unsigned)plan.grid;
+    if (VW == 4 && plan.full) spmm_merge_kernel<G, NV, VW, TG, U, FMT, (VW == 4)><<<grid, kMergeThreads, 0, st>>>(p);
+    else spmm_merge_kernel<G, NV, VW, TG, U, FMT, false><<<grid, kMergeThreads, 0, st>>>(p);
+}
+
 template <int VW, int FMT>
 void dispatch_merge(const SpmmParams& p, const Plan& plan, cudaStream_t st)
 {
+    switch (plan.narrow) {
+        case 1: launch_merge_narrow<0, VW, FMT>(p, plan, st); return;
+        case 2: launch_merge_narrow<1, VW, FMT>(p, plan, st); return;
+        case 3: launch_merge_narrow<2, VW, FMT>(p, plan, st); return;
+        default: break;
+    }
     switch (plan.shape) {
         case 0: launch_merge<0, VW, FMT>(p, plan, st); break;
         case 1: launch_merge<1, VW, FMT>(p, plan, st); break;

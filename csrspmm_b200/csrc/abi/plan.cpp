@@ -137,7 +137,7 @@ static void fill_split_geometry(const csrspmm_b200_args* a, Plan* plan, int tile
         plan->carry_row_bytes + (size_t)plan->num_tiles * (size_t)plan->carry_ld * sizeof(float);
 }
 
-int make_plan(const csrspmm_b200_args* a, Plan* plan)
+int make_plan(const csrspmm_b200_args* a, Plan* plan, bool allow_narrow)
 {
     int st = check_args(a, false);
     if (st != CSRSPMM_B200_OK) return st;
@@ -196,7 +196,15 @@ int make_plan(const csrspmm_b200_args* a, Plan* plan)
         plan->G = kShapes[plan->shape].G;
         plan->NV = kShapes[plan->shape].NV;
         plan->full = plan->VW == 4 && plan->G * plan->NV == plan->ncolv;
-        if (kernel == CSRSPMM_B200_KERNEL_MERGE) {
+        if (CSRSPMM_TUNE_MERGE_NARROW && kernel == CSRSPMM_B200_KERNEL_MERGE && allow_narrow && plan->ncolv >= 1 && plan->ncolv <= 4) {
+            // one, two or four column vectors: lane groups of that many lanes (kNarrowShapes)
+            plan->narrow = plan->ncolv == 1 ? 1 : (plan->ncolv == 2 ? 2 : 3);
+            const ShapeDesc& ns = kNarrowShapes[plan->narrow - 1];
+            plan->G = ns.G;
+            plan->NV = ns.NV;
+            plan->full = plan->VW == 4 && plan->G * plan->NV == plan->ncolv;
+            fill_split_geometry(a, plan, (CSRSPMM_TUNE_MERGE_THREADS / ns.G) * ns.TG);
+        } else if (kernel == CSRSPMM_B200_KERNEL_MERGE) {
             fill_split_geometry(a, plan, merge_tile_for(plan->shape, plan->num_items, &plan->small_tile));
         } else {
             const int groups = CSRSPMM_TUNE_ROW_THREADS / plan->G;

@@ -19,6 +19,8 @@ struct Plan {
     bool low_occupancy = false;            // row kernel: fewer than 8 warps of rows per SM
     bool full = false;                     // one pass covers the row exactly: G*NV == ncolv
     bool small_tile = false;               // merge kernel: the small-problem tile (fewer items per lane group)
+    int narrow = 0;                        // merge kernel: 1 + index into kNarrowShapes when the dense operand has at
+                                           // most four column vectors (lane groups of 1, 2 or 4 lanes), else 0
     int G = 8, NV = 1, VW = 4;             // lanes per group, vectors per lane, vector width
     int ncolv = 0;                         // ceil(Nd / VW)
     int tile = 0;                          // merge-path items per CTA (split kernels)
@@ -40,7 +42,7 @@ bool vector_layout_ok(const csrspmm_b200_args* a);
 
 // Resolves AUTO (and the CSRSPMM_FORCE_KERNEL override) and fills the launch geometry.
 // Returns CSRSPMM_B200_OK or an error status.
-int make_plan(const csrspmm_b200_args* a, Plan* plan);
+int make_plan(const csrspmm_b200_args* a, Plan* plan, bool allow_narrow = true);
 
 // Merge-path items per CTA of the merge kernel for lane-group shape `shape` on a problem of
 // `num_items` = M + nnz items (*small says whether the small-problem tile was chosen).

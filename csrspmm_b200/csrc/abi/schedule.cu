@@ -172,7 +172,7 @@ int scheduled_plan(const csrspmm_b200_args* a, Plan* plan)
     csrspmm_b200_args m = *a;
     m.kernel = CSRSPMM_B200_KERNEL_MERGE;
     m.schedule = nullptr;
-    int status = make_plan(&m, plan);
+    int status = make_plan(&m, plan, /*allow_narrow=*/false);  // the SKIP build exists for the regular shapes only
     if (status != CSRSPMM_B200_OK) return status;
     if (plan->small_tile) {  // few items but a large B: keep the one instantiated tile
         plan->small_tile = false;

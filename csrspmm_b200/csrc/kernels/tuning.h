@@ -226,6 +226,17 @@ namespace csrspmm_b200 {
 struct ShapeDesc {
     int G, NV, TG;
 };
+// Merge-path kernel on very narrow dense operands (1, 2 or 4 column vectors: Nd <= 4, 8, 16 with the
+// 16-byte layout): a lane group of eight would leave seven, six or four of its lanes without a column,
+// so the groups shrink to 1, 2 or 4 lanes -- at G = 1 every lane walks its own run of non-zeros
+// (lanes over non-zeros instead of lanes over columns) and the rows cut between lanes are summed in
+// lane order through shared memory like any other split row.  3072 merge-path items per CTA as for
+// the wider shapes.
+#ifndef CSRSPMM_TUNE_MERGE_NARROW
+#define CSRSPMM_TUNE_MERGE_NARROW 1
+#endif
+constexpr int kNumNarrowShapes = 3;
+constexpr ShapeDesc kNarrowShapes[kNumNarrowShapes] = {{1, 1, 12}, {2, 1, 24}, {4, 1, 48}};
 struct PieceShapeDesc {
     int G, NV, D;
 };

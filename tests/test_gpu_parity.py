@@ -5,6 +5,7 @@ sequential fused oracle bit for bit (always the case for the row kernel); everyt
 rtol 1e-5 / atol 1e-6 against it, except rows that the split kernels cut into pieces, which
 are judged against the fp64 oracle with |err| <= 1e-5 * sum|a*b| + 1e-6.
 """
+import os
 from pathlib import Path
 
 import numpy as np
@@ -21,6 +22,8 @@ SMALL = sorted(p.stem for p in GOLDEN.glob("*.npz") if p.stem != "cfg1_check")
 KERNELS = ["row", "merge", "tma"]
 ENTRIES = ["naive", "naive_smem", "warp_per_row", "warp_per_row_fp4", "warp_per_row_smem", "warp_per_row_smem_fp4"]
 RTOL, ATOL = 1e-5, 1e-6
+# strict elementwise pass rate demanded of results that contain rows cut into pieces (see assert_parity)
+STRICT_FLOOR = 0.99  # lowest measured over this file: 0.9935 (config 4 at 1/16, bulk-copy kernel)
 
 
 def dev(x):
@@ -49,13 +52,21 @@ def assert_parity(got, rp, ci, va, B, C0=None, alpha=1.0, beta=0.0, exact=False)
     f64, mag = oracle.spmm_f64(rp, ci, va, B, C0, alpha, beta, threads=4)
     err = np.abs(got.astype(np.float64) - f64)
     assert (err <= RTOL * mag + ATOL).all(), f"worst excess {(err - RTOL * mag - ATOL).max()}"
+    # measured: no result of this file uses more than 0.032 of that bound; a quarter of it is demanded
+    assert (err <= 0.25 * (RTOL * mag + ATOL)).all(), f"worst err / bound {(err / (RTOL * mag + ATOL)).max()}"
     # Elementwise rtol/atol against the sequential oracle: only elements of rows that were cut
     # into pieces (re-associated sums; near-cancelling outputs) may miss it.  A row is cut at
     # most every 64 merge-path items, so the share of such elements is bounded by the share of
-    # rows longer than that, and in practice far smaller.
+    # rows longer than that, and in practice far smaller (CSRSPMM_PARITY_LOG=<file> records the rate
+    # and the worst error of every check).
     close = np.isclose(got, want, rtol=RTOL, atol=ATOL)
     lens = np.diff(np.asarray(rp, np.int64))
-    floor = 0.999 if lens.size == 0 or lens.max() <= 64 else 0.97
+    log = os.environ.get("CSRSPMM_PARITY_LOG")
+    if log:  # one line per check: strict pass rate and worst error in units of the bound
+        with open(log, "a") as f:
+            f.write(f"{os.environ.get('PYTEST_CURRENT_TEST', '?')} rate {close.mean():.6f} worst {float((err / (RTOL * mag + ATOL)).max()):.4f} "
+                    f"maxrow {int(lens.max()) if lens.size else 0}\n")
+    floor = 0.999 if lens.size == 0 or lens.max() <= 64 else STRICT_FLOOR
     assert close.mean() > floor, f"elementwise pass rate {close.mean()}"
 
 
@@ -146,6 +157,24 @@ def test_dense_widths(cuda_lib, Nd, kernel):
     C0 = np.random.default_rng(Nd).standard_normal((p.M, Nd), dtype=np.float32)
     got = run(arrays(p), kernel, C0, 0.75, -1.25)
     assert_parity(got, *arrays(p), C0, 0.75, -1.25, exact=(kernel == "row"))
+
+
+@pytest.mark.parametrize("Nd", [1, 2, 3, 4, 6, 8, 11, 12, 16])
+def test_very_narrow_dense_operands_on_skewed_rows(cuda_lib, Nd):
+    """One to four column vectors: the merge-path kernel runs lane groups of 1, 2 or 4 lanes (every lane its
+    own run of non-zeros at Nd <= 4), with hub rows cut across hundreds of lanes and CTAs, empty rows, and
+    packed 4-bit values."""
+    lens = G.zipf_lengths(np.random.default_rng(Nd), 6000, 20000, 2.0, 12.0, 9000)
+    lens[::5] = 0
+    p = G.from_lengths("narrow", lens, 20000, Nd, np.random.default_rng(Nd + 1), -1.0, 1.0, Nd)
+    C0 = np.random.default_rng(Nd).standard_normal((p.M, Nd), dtype=np.float32)
+    got = run(arrays(p), "merge", C0, 1.5, 0.5)
+    assert_parity(got, *arrays(p), C0, 1.5, 0.5)
+    assert np.array_equal(got, run(arrays(p), "merge", C0, 1.5, 0.5))  # fixed summation order
+    packed, scale = ops.e2m1_quantize(p.values)
+    decoded = oracle.e2m1_decode(packed.numpy(), p.nnz, scale)
+    got4 = run((p.row_ptr, p.col_idx, packed.numpy(), p.B), "merge", e2m1_scale=scale, nnz=p.nnz)
+    assert np.array_equal(got4, run((p.row_ptr, p.col_idx, decoded, p.B), "merge"))
 
 
 @pytest.mark.parametrize("kernel", KERNELS)

@@ -58,7 +58,7 @@ def test_scheduled_product_matches_the_oracle(cuda_lib, Nd):
     got = run(p, s)
     check(got, p)
     want = oracle.spmm(p.row_ptr, p.col_idx, p.values, p.B, fused=True, threads=4)
-    assert np.isclose(got, want, rtol=RTOL, atol=ATOL).mean() > 0.97
+    assert np.isclose(got, want, rtol=RTOL, atol=ATOL).mean() > 0.99
     assert np.array_equal(got, run(p, s))  # fixed summation order
     C0 = np.random.default_rng(5).standard_normal((p.M, Nd), dtype=np.float32)
     check(run(p, s, C0, 1.5, 0.5), p, C0, 1.5, 0.5)
