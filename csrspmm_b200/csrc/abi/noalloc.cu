@@ -13,10 +13,10 @@
 // Limits and rules.
 //   * The array is CSRSPMM_B200_NOALLOC_SCRATCH_BYTES (8 MiB) per device and exists on every GPU
 //     that loads the library, until the process ends.  A problem that needs more (one int32 plus
-//     one row of Nd floats per CTA of the merge kernel, i.e. per 512 to 3072 merge-path items) is refused with ERR_WORKSPACE and a
-//     message that states both numbers; nothing is launched.
-//   * It always runs the merge-path kernel (args.kernel, args.workspace, args.workspace_bytes
-//     are ignored).
+//     one row of Nd floats per CTA of the merge kernel, i.e. per 512 to 3072 merge-path items) is
+//     refused with ERR_WORKSPACE and a message that states both numbers; nothing is launched.
+//   * It always runs the merge-path kernel (args.kernel, args.workspace, args.workspace_bytes and
+//     args.schedule are ignored).
 //   * All calls on one device share the one array.  It keeps whatever the previous call left, and
 //     that is harmless: every slot the fix-up kernel reads (one carry row index per CTA, and the
 //     carry values of the CTAs whose index is valid) is rewritten by the same call's main kernel

@@ -155,7 +155,7 @@ int make_plan(const csrspmm_b200_args* a, Plan* plan, bool allow_narrow)
         if (kernel == CSRSPMM_B200_KERNEL_TMA && !tma_can_run(a)) kernel = CSRSPMM_B200_KERNEL_AUTO;
     }
     if (kernel == CSRSPMM_B200_KERNEL_AUTO) {
-        // Measured on B200 (profiles/): the bulk-copy path completes about one row copy per 80
+        // Measured on B200: the bulk-copy path completes about one row copy per 80
         // cycles per SM, so it only keeps HBM busy when a row of B is 2 KB (384 < Nd <= 512),
         // where it is 3-4 % ahead of the merge kernel -- provided B is far larger than L2, since
         // an L2-resident B is served faster through the load/store units.  Whole-row mapping
