@@ -259,14 +259,12 @@ int enqueue_scheduled(const csrspmm_b200_args* a, cudaStream_t st)
     q.pieces = s->pieces;
     q.num_pieces = (int)s->num_pieces;
     q.pieces_per_group = CSRSPMM_TUNE_SLICED_PIECES_PER_GROUP;
-    if (const int e = env_int("CSRSPMM_SCHED_PPG")) q.pieces_per_group = e > 0 && e <= 16 ? e : q.pieces_per_group;
     q.piece_cap = s->piece_nnz;
     q.slots = reinterpret_cast<float*>(static_cast<char*>(ws) + plan.workspace_bytes);
     q.slot_ld = (long long)slot_ld;
     q.long_rows = s->long_rows;
     q.num_long_rows = s->num_long;
     q.evict_last = CSRSPMM_TUNE_SLICED_EVICT_LAST;
-    if (const char* e = std::getenv("CSRSPMM_SCHED_EVICT_LAST")) q.evict_last = std::atoi(e);
 
     const bool e2m1 = a->value_format == CSRSPMM_B200_VALUES_E2M1;
     const long long per_cta = (long long)(kSlicedThreads / kPieceShapes[plan.shape].G) * q.pieces_per_group;
