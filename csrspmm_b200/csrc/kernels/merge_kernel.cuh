@@ -323,12 +323,12 @@ __global__ void __launch_bounds__(kMergeThreads, merge_min_blocks(NV)) spmm_merg
         };
 
         int base = r.jl0;
-        if constexpr (SKIP) {
+        if constexpr (SKIP || CSRSPMM_TUNE_MERGE_ONE_LOOP) {
             // as below, but a scheduled row is jumped over: to its end when that lies in this
             // group's range (rows before il1 end at or before jl1), else to the end of the range
             while (base < r.jl1) {
                 while (base >= next_end) finish_row();  // an entry exists at `base`, so these ends are mine
-                if (skip) {
+                if (SKIP && skip) {
                     if (i < r.il1) {
                         base = next_end;
                         finish_row();
@@ -360,7 +360,7 @@ __global__ void __launch_bounds__(kMergeThreads, merge_min_blocks(NV)) spmm_merg
                     for (int u = 0; u < U; ++u) {
                         if (u < n) {
                             while (base + u >= next_end) finish_row();
-                            if (!skip) {
+                            if (!(SKIP && skip)) {
                                 const float a = __int_as_float(e[u].y);
 #pragma unroll
                                 for (int v = 0; v < NV; ++v) acc[v].fma(a, bq[u][v]);

@@ -83,6 +83,12 @@
 #define CSRSPMM_TUNE_P4_D 4
 #endif
 
+// merge-path kernel: walk a lane group's range with one loop (loads predicated on the batch length)
+// instead of a loop of whole batches followed by the partial one
+#ifndef CSRSPMM_TUNE_MERGE_ONE_LOOP
+#define CSRSPMM_TUNE_MERGE_ONE_LOOP 0
+#endif
+
 // threads per CTA of the merge-path kernels (merge, bulk-copy): lane groups per CTA = this / G
 #ifndef CSRSPMM_TUNE_MERGE_THREADS
 #define CSRSPMM_TUNE_MERGE_THREADS 256
