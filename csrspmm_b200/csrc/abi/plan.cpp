@@ -214,7 +214,7 @@ int make_plan(const csrspmm_b200_args* a, Plan* plan, bool allow_narrow)
             // many short rows: a CTA that lives for four 16-entry rows costs more to start than to
             // run (cfg2: 20.5 -> 18.6 us; 65536 rows of 13: 53 -> 45 us; long rows prefer the
             // finer dynamic balance of one CTA per few rows)
-            if (a->nnz <= 64 * (long long)a->M && plan->grid > 148LL * CSRSPMM_TUNE_ROW_PERSISTENT)
+            if (a->nnz <= (long long)CSRSPMM_TUNE_ROW_PERSISTENT_MAX_MEAN * (long long)a->M && plan->grid > 148LL * CSRSPMM_TUNE_ROW_PERSISTENT)
                 plan->grid = 148LL * CSRSPMM_TUNE_ROW_PERSISTENT;
 #endif
         }

@@ -128,6 +128,11 @@
 #define CSRSPMM_TUNE_ROW_PERSISTENT 8
 #endif
 
+// ... for matrices whose mean row length is at most this
+#ifndef CSRSPMM_TUNE_ROW_PERSISTENT_MAX_MEAN
+#define CSRSPMM_TUNE_ROW_PERSISTENT_MAX_MEAN 64
+#endif
+
 // threads per CTA of the row kernel (128: 4 rows per CTA at G = 32; small CTAs keep the tail short
 // when there are only a few thousand rows -- 4096 rows in 256-thread CTAs left a 15 % imbalance)
 #ifndef CSRSPMM_TUNE_ROW_THREADS
