@@ -79,6 +79,11 @@ constexpr int kDefaultPiece = 64;
 // rows out leaves that chain exposed.  Config 3 (256-byte rows): 653 us without a schedule, 1.0-1.5 ms
 // with one at any threshold, although its pieces read 0.49 GB from HBM instead of 2.4 GB.
 constexpr size_t kMinRowBytesForAuto = 1024;
+// ... and nothing when the scheduled rows together name each row of B fewer than this many times: what the
+// pieces save is the re-use of a slab's rows while it sits in L2, and a row block of a matrix cut across N
+// GPUs has 1/N of the re-use (config 5: 6.4 / 3.2 / 1.6 / 0.8 entries per row of B on 1 / 2 / 4 / 8 GPUs;
+// 40.6 -> 38.3 ms and 20.4 -> 19.3 ms at 1 and 2 GPUs, 10.2 -> 10.1 ms at 4).
+constexpr double kMinReuseForAuto = 2.0;
 
 bool valid(const csrspmm_b200_schedule* s) { return s != nullptr && s->magic == kScheduleMagic; }
 
@@ -358,6 +363,7 @@ int csrspmm_b200_schedule_create(const csrspmm_b200_args* a, const csrspmm_b200_
     // a B that fits one slab is served from L2 whatever the order: nothing to schedule
     const bool pointless = num_slabs <= 1;
     bool pointless_auto = false;
+    const bool auto_threshold = threshold <= 0;
     if (threshold <= 0) {
         const long long t = (long long)kMinEntriesPerSlab * num_slabs;
         threshold = t > 0x3fffffff ? 0x3fffffff : (int)t;
@@ -425,6 +431,7 @@ int csrspmm_b200_schedule_create(const csrspmm_b200_args* a, const csrspmm_b200_
         if (num_long > capacity) num_long = capacity;  // only a malformed row_ptr gets here
         unsigned long long long_nnz = 0;
         std::memcpy(&long_nnz, &h_counters[2], sizeof(long_nnz));
+        if (auto_threshold && (double)long_nnz < kMinReuseForAuto * (double)Kd) num_long = 0;  // too little re-use of B
 
         if (num_long > 0) {
             const size_t bounds_bytes = (size_t)num_long * (size_t)(num_slabs + 1) * sizeof(int);
