@@ -20,9 +20,9 @@ ERR_BAD_ARG, ERR_INVALID_CSR, ERR_UNSUPPORTED, ERR_CUDA, ERR_DEVICE_WAIT, ERR_WO
 
 ENTRY_NAIVE, ENTRY_NAIVE_SMEM, ENTRY_WARP_PER_ROW, ENTRY_WARP_PER_ROW_FP4, ENTRY_WARP_PER_ROW_SMEM, \
     ENTRY_WARP_PER_ROW_SMEM_FP4 = range(6)
-KERNEL_AUTO, KERNEL_ROW, KERNEL_MERGE, KERNEL_TMA = range(4)
-KERNEL_NAMES = {KERNEL_AUTO: "auto", KERNEL_ROW: "row", KERNEL_MERGE: "merge", KERNEL_TMA: "tma"}
-KERNEL_IDS = {v: k for k, v in KERNEL_NAMES.items()}
+KERNEL_AUTO, KERNEL_ROW, KERNEL_MERGE, KERNEL_TMA, KERNEL_SCHEDULED = range(5)
+KERNEL_NAMES = {KERNEL_AUTO: "auto", KERNEL_ROW: "row", KERNEL_MERGE: "merge", KERNEL_TMA: "tma", KERNEL_SCHEDULED: "scheduled"}
+KERNEL_IDS = {v: k for k, v in KERNEL_NAMES.items() if k != KERNEL_SCHEDULED}  # "scheduled" is an answer, never an input
 VALUES_F32, VALUES_E2M1 = 0, 1
 NOALLOC_SCRATCH_BYTES = 8 << 20
 

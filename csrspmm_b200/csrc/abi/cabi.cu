@@ -429,6 +429,7 @@ int csrspmm_b200_select_kernel(const csrspmm_b200_args* args)
     Plan plan;
     int status = make_plan(args, &plan);
     if (status != CSRSPMM_B200_OK) return -status;
+    if (schedule_applies(args)) return CSRSPMM_B200_KERNEL_SCHEDULED;
     return plan.kernel;
 }
 

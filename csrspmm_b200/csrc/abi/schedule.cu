@@ -198,8 +198,17 @@ namespace csrspmm_b200 {
 
 bool schedule_applies(const csrspmm_b200_args* a)
 {
-    return a != nullptr && valid(a->schedule) && a->schedule->num_long > 0 && a->schedule->num_pieces > 0 &&
-           !env_forces_other_kernel();
+    if (a == nullptr || !valid(a->schedule) || a->schedule->num_long <= 0 || a->schedule->num_pieces <= 0 ||
+        env_forces_other_kernel())
+        return false;
+    if (a->kernel == CSRSPMM_B200_KERNEL_AUTO) {
+        // rows known to be even: the whole-row kernel is what AUTO would run, and it is the better choice
+        csrspmm_b200_args plain = *a;
+        plain.schedule = nullptr;
+        Plan plan;
+        if (make_plan(&plain, &plan) == CSRSPMM_B200_OK && plan.kernel == CSRSPMM_B200_KERNEL_ROW) return false;
+    }
+    return true;
 }
 
 size_t scheduled_workspace_bytes(const csrspmm_b200_args* a)

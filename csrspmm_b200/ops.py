@@ -156,7 +156,7 @@ def spmm(row_ptr, col_idx, values, B, C_out=None, alpha=1.0, beta=0.0, *, entry=
             chosen = L.csrspmm_b200_select_kernel(C.byref(a))
             if chosen < 0:
                 raise _lib.SpmmError(-chosen, "csrspmm_b200_select_kernel")
-            if chosen != _lib.KERNEL_ROW or schedule is not None:
+            if chosen != _lib.KERNEL_ROW:
                 need = int(L.csrspmm_b200_workspace_bytes(C.byref(a)))
                 if workspace is None or workspace.numel() * workspace.element_size() < need:
                     workspace = torch.empty(max(need, 256), dtype=torch.uint8, device=B.device)
@@ -241,11 +241,9 @@ class SpmmCall:
             if k < 0:
                 raise _lib.SpmmError(-k, "csrspmm_b200_select_kernel")
             self.kernel = _lib.KERNEL_NAMES[k]
-            self.launches = 1 if k == _lib.KERNEL_ROW else 2
-            if schedule is not None and schedule.active and kernel in ("auto", "merge"):
-                self.kernel = "scheduled"  # pieces, slot sums, merge-path over the other rows, fix-up
-                self.launches = 4
-            if k != _lib.KERNEL_ROW or self.kernel == "scheduled":
+            # scheduled: pieces, slot sums, merge-path over the other rows, fix-up
+            self.launches = 1 if k == _lib.KERNEL_ROW else (4 if k == _lib.KERNEL_SCHEDULED else 2)
+            if k != _lib.KERNEL_ROW:
                 need = int(self.L.csrspmm_b200_workspace_bytes(C.byref(self.args)))
                 if workspace is None or workspace.numel() * workspace.element_size() < need:
                     workspace = torch.empty(max(need, 256), dtype=torch.uint8, device=B.device)

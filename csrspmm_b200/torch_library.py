@@ -9,8 +9,8 @@ The reference's Python ops are plain pybind functions (torch_csrspmm/binding.cpp
   ``dB = alpha * A^T @ dC`` (A^T built once per matrix as a CSR, by a stable sort on the device);
 * ``torch.ops.csrspmm_b200.spmm_(row_ptr, col_idx, values, B, C, alpha, beta, kernel)`` -> in place
   ``C = alpha * A @ B + beta * C`` (the reference's full semantics);
-* ``CsrMatrix``: keeps the three arrays, the longest row (so AUTO can pick the row kernel) and the
-  cached transpose together.
+* ``CsrMatrix``: keeps the three arrays, the longest row (so AUTO can pick the row kernel), the cached
+  transpose and, per dense width, the matrix's schedule (``csrspmm_b200_schedule_create``) together.
 
 Gradients with respect to the stored values of A (a sampled dense-dense product) are not provided.
 """
@@ -86,6 +86,21 @@ class CsrMatrix:
             ops.validate_csr(row_ptr, col_idx, self.shape[1])
         self.max_row_nnz = ops.row_stats(row_ptr)["max_row_nnz"] if row_ptr.is_cuda else 0
         self._t = None
+        self._schedules = {}  # dense width -> ops.Schedule or None (built on first use, kept with the matrix)
+
+    def schedule(self, Nd: int):
+        """The per-matrix schedule for a B of ``Nd`` columns, built on first use (a few milliseconds) and kept;
+        None when the library finds nothing worth scheduling for this matrix and width."""
+        Nd = int(Nd)
+        if Nd not in self._schedules:
+            sched = None
+            if self.row_ptr.is_cuda and self.nnz > 0:
+                sched = ops.Schedule(self.row_ptr, self.col_idx, self.shape[1], Nd)
+                if not sched.active:
+                    sched.close()
+                    sched = None
+            self._schedules[Nd] = sched
+        return self._schedules[Nd]
 
     @property
     def nnz(self) -> int:
@@ -104,7 +119,7 @@ class CsrMatrix:
         if out is None and B.requires_grad:
             return _CsrMatmul.apply(self, B, float(alpha), kernel)
         return ops.spmm(self.row_ptr, self.col_idx, self.values, B, out, alpha, beta, kernel=kernel,
-                        max_row_nnz=self.max_row_nnz)
+                        max_row_nnz=self.max_row_nnz, schedule=self.schedule(B.shape[1]) if kernel == "auto" else None)
 
     __matmul__ = matmul
 
@@ -116,11 +131,11 @@ class _CsrMatmul(torch.autograd.Function):
     def forward(ctx, A: CsrMatrix, B: torch.Tensor, alpha: float, kernel: str):
         ctx.A, ctx.alpha, ctx.kernel = A, alpha, kernel
         return ops.spmm(A.row_ptr, A.col_idx, A.values, B.contiguous(), None, alpha, 0.0, kernel=kernel,
-                        max_row_nnz=A.max_row_nnz)
+                        max_row_nnz=A.max_row_nnz, schedule=A.schedule(B.shape[1]) if kernel == "auto" else None)
 
     @staticmethod
     def backward(ctx, grad_C):
         At = ctx.A.t()
         dB = ops.spmm(At.row_ptr, At.col_idx, At.values, grad_C.contiguous(), None, ctx.alpha, 0.0, kernel=ctx.kernel,
-                      max_row_nnz=At.max_row_nnz)
+                      max_row_nnz=At.max_row_nnz, schedule=At.schedule(grad_C.shape[1]) if ctx.kernel == "auto" else None)
         return None, dB, None, None

@@ -69,8 +69,11 @@ typedef enum csrspmm_b200_kernel {
     CSRSPMM_B200_KERNEL_AUTO = 0,
     CSRSPMM_B200_KERNEL_ROW = 1,    /* lane group per row; sequential accumulation per output */
     CSRSPMM_B200_KERNEL_MERGE = 2,  /* merge-path split over (rows + nnz); carries + fix-up */
-    CSRSPMM_B200_KERNEL_TMA = 3     /* merge-path split, B rows staged through shared memory by
+    CSRSPMM_B200_KERNEL_TMA = 3,    /* merge-path split, B rows staged through shared memory by
                                        bulk async copies (needs the 16-byte-aligned layout) */
+    CSRSPMM_B200_KERNEL_SCHEDULED = 4 /* answer of csrspmm_b200_select_kernel only, never an input: the
+                                       product will run under args.schedule (pieces, slot sums, merge-path
+                                       kernel over the other rows) */
 } csrspmm_b200_kernel;
 
 typedef enum csrspmm_b200_value_format {
@@ -222,7 +225,8 @@ int csrspmm_b200_select_kernel(const csrspmm_b200_args* args);
  * as long as row_ptr and col_idx are unchanged (values, B, C, alpha, beta and Nd may change; Nd
  * only moves the slab size away from the one planned).  A call whose M, Kd or nnz differ from the
  * schedule's is refused with ERR_BAD_ARG.  args.kernel must be AUTO or MERGE and args.row_ptr_base
- * 0.  Scratch: csrspmm_b200_workspace_bytes(args) with args.schedule set.  Thread-safe for
+ * 0; with AUTO the schedule is left aside when the rows are known to be even (args.max_row_nnz close to
+ * the mean), where the whole-row kernel is the better choice.  Scratch: csrspmm_b200_workspace_bytes(args) with args.schedule set.  Thread-safe for
  * concurrent products as long as each has its own workspace. */
 struct csrspmm_b200_schedule;
 typedef struct csrspmm_b200_schedule csrspmm_b200_schedule;

@@ -176,6 +176,32 @@ def test_prepared_call_with_a_schedule(cuda_lib):
     assert torch.equal(first, out)
 
 
+def test_even_rows_keep_the_whole_row_kernel(cuda_lib):
+    """With AUTO and a longest row known to be close to the mean, the whole-row kernel is the better choice and
+    a schedule is left aside; csrspmm_b200_select_kernel says which way a call will go."""
+    p = G.random_csr(2000, 8192, 64, 0.0, seed=3, lengths=np.full(2000, 40))
+    rp, ci, va, B = dev(p.row_ptr), dev(p.col_idx), dev(p.values), dev(p.B)
+    s = ops.Schedule(rp, ci, p.Kd, 64, threshold=16, slab_rows=1024)
+    assert s.active
+    out = torch.empty(p.M, 64, device="cuda")
+    assert ops.SpmmCall(rp, ci, va, B, out, schedule=s).kernel == "scheduled"  # row lengths unknown
+    known = ops.SpmmCall(rp, ci, va, B, out, schedule=s, max_row_nnz=40)
+    assert known.kernel == "row" and known.launches == 1
+    known()
+    torch.cuda.synchronize()
+    assert np.array_equal(out.cpu().numpy(), oracle.spmm(p.row_ptr, p.col_idx, p.values, p.B, fused=True, threads=4))
+    assert ops.SpmmCall(rp, ci, va, B, out, schedule=s, max_row_nnz=40, kernel="merge").kernel == "scheduled"
+
+
+def test_csr_matrix_keeps_its_schedules(cuda_lib):
+    from csrspmm_b200.torch_library import CsrMatrix
+    p = skewed(4096, 8192, 320, seed=31, mean=40.0)
+    A = CsrMatrix(dev(p.row_ptr), dev(p.col_idx), dev(p.values), (p.M, p.Kd))
+    assert A.schedule(320) is None and A.schedule(320) is None  # B of 10 MB: one slab, nothing to schedule; asked once
+    got = (A @ dev(p.B)).cpu().numpy()
+    check(got, p)
+
+
 def test_cfg3_powerlaw_full_size_under_its_schedule(cuda_lib):
     """BASELINE config 3 at full size under a schedule (threshold given: for rows of B this narrow the
     library would schedule nothing by itself): oracle on a row sample (random rows and the longest ones), row
