@@ -139,7 +139,10 @@ __global__ void __launch_bounds__(kSlicedThreads, MINB) spmm_sliced_kernel(const
 #pragma unroll
             for (int v = 0; v < NV; ++v) {
                 const int cv = cb + lane + v * G;
-                if (FULL || cv < p.ncolv) acc[v].store(slot + (long long)cv * VW);
+                if (FULL || cv < p.ncolv) {
+                    if (CSRSPMM_TUNE_SLICED_STREAM_SLOTS) acc[v].store_streaming(slot + (long long)cv * VW);
+                    else acc[v].store(slot + (long long)cv * VW);
+                }
             }
         };
 

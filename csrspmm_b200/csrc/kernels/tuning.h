@@ -32,6 +32,11 @@
 #ifndef CSRSPMM_TUNE_SLICED_EVICT_LAST
 #define CSRSPMM_TUNE_SLICED_EVICT_LAST 0
 #endif
+// scheduled pieces write their slots with streaming stores (1) or plain ones (0): the slots are read
+// back by another kernel and should not push the slab of B out of L2
+#ifndef CSRSPMM_TUNE_SLICED_STREAM_SLOTS
+#define CSRSPMM_TUNE_SLICED_STREAM_SLOTS 0
+#endif
 
 // Scheduled pieces (sliced_kernel.cuh): the gather is pipelined through shared memory, no gathered
 // row is held in registers, so a lane can own more column vectors and a warp more pieces.  Per dense
