@@ -152,6 +152,15 @@ struct Vec<4> {
     __device__ __forceinline__ void load(const float* p) { v = *reinterpret_cast<const float4*>(p); }
     __device__ __forceinline__ void store(float* p) const { *reinterpret_cast<float4*>(p) = v; }
     __device__ __forceinline__ void store_streaming(float* p) const { __stcs(reinterpret_cast<float4*>(p), v); }
+    __device__ __forceinline__ Vec shuffle(int src_lane) const  // this value as held by src_lane of the warp
+    {
+        Vec r;
+        r.v.x = __shfl_sync(0xffffffffu, v.x, src_lane);
+        r.v.y = __shfl_sync(0xffffffffu, v.y, src_lane);
+        r.v.z = __shfl_sync(0xffffffffu, v.z, src_lane);
+        r.v.w = __shfl_sync(0xffffffffu, v.w, src_lane);
+        return r;
+    }
     __device__ __forceinline__ void fma(float a, const Vec& b)
     {
         v.x = __fmaf_rn(a, b.v.x, v.x);
@@ -218,6 +227,12 @@ struct Vec<1> {
     __device__ __forceinline__ void load(const float* p) { v = *p; }
     __device__ __forceinline__ void store(float* p) const { *p = v; }
     __device__ __forceinline__ void store_streaming(float* p) const { __stcs(p, v); }
+    __device__ __forceinline__ Vec shuffle(int src_lane) const
+    {
+        Vec r;
+        r.v = __shfl_sync(0xffffffffu, v, src_lane);
+        return r;
+    }
     __device__ __forceinline__ void fma(float a, const Vec& b) { v = __fmaf_rn(a, b.v, v); }
     __device__ __forceinline__ void add(const Vec& b) { v = __fadd_rn(v, b.v); }
     __device__ __forceinline__ Vec epilogue(float alpha, float beta, const Vec& old) const

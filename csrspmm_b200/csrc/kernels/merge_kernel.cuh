@@ -104,6 +104,7 @@ template <class Smem, int G, int TG, int FMT, bool SKIP = false>
 __device__ __forceinline__ bool merge_tile_setup(const SpmmParams& p, Smem& s, TileRange& r)
 {
     constexpr int TILE = Smem::TILE;
+    constexpr int SB = CSRSPMM_TUNE_MERGE_STAGE_BATCH;
     const int tid = threadIdx.x;
     const int warp = tid >> 5;
     const int* __restrict__ row_end = p.row_ptr + 1;
@@ -133,48 +134,93 @@ __device__ __forceinline__ bool merge_tile_setup(const SpmmParams& p, Smem& s, T
     }
 
     // ---- 2. stage the slice ----------------------------------------------------------------
-    if constexpr (SKIP) {
-        for (int k0 = warp * 32; k0 <= r.nrows; k0 += kMergeThreads) {  // whole warps: one flag word each
-            const int k = k0 + (tid & 31);
-            bool is_long = false;
-            if (k <= r.nrows) {
-                const long long gi = (long long)r.i0 + k;
-                int end = 0;
-                if (gi < p.M) {
-                    end = __ldg(row_end + gi);
-                    is_long = end - __ldg(p.row_ptr + gi) >= p.skip_len;
-                }
-                s.rowend[k] = (k < r.nrows) ? (end - p.rp_base - r.j0) : INT_MAX;
-            }
-            const unsigned bits = __ballot_sync(0xffffffffu, is_long);
-            if ((tid & 31) == 0) s.longbits[k0 >> 5] = bits;
-        }
-        __syncthreads();
-    } else {
-        for (int k = tid; k <= r.nrows; k += kMergeThreads)
-            s.rowend[k] = (k < r.nrows) ? (__ldg(row_end + r.i0 + k) - p.rp_base - r.j0) : INT_MAX;
-    }
-    for (int k = tid; k < r.nnzt; k += kMergeThreads) {
-        if constexpr (SKIP) {
-            // the row that holds the first entry of this warp's run of 32
-            const int k0 = k & ~31;
-            int lo = 0, hi = r.nrows;
-            while (lo < hi) {
-                const int mid = (lo + hi) >> 1;
-                if (s.rowend[mid] <= k0) lo = mid + 1;
-                else hi = mid;
-            }
-            if (s.is_long(lo) && s.rowend[lo] >= min(k0 + 32, r.nnzt)) {
-                s.cv[k] = make_int2(0, 0);  // never read as data, but a batch may gather row 0 of B for it
-                continue;
-            }
-        }
-        int c = __ldcs(p.col_idx + r.j0 + k);
+    // SB global loads in flight per thread and list, then the stores to shared memory: a load-store
+    // pair per iteration would make the staging a chain of TILE / kMergeThreads round trips to memory.
+    auto clamp_col = [&](int c) {
         if ((unsigned)c >= (unsigned)p.Kd) {  // never fault on a bad index
             c = min(max(c, 0), p.Kd - 1);
             report_status(p, kStatusColClamped);
         }
-        s.cv[k] = make_int2(c, __float_as_int(load_value<FMT>(p.values, r.j0 + k, p.value_scale)));
+        return c;
+    };
+    if constexpr (SKIP) {
+        for (int k0 = warp * 32; k0 <= r.nrows; k0 += kMergeThreads * SB) {  // whole warps: one flag word each
+            int end[SB], beg[SB];
+#pragma unroll
+            for (int b = 0; b < SB; ++b) {
+                const long long gi = (long long)r.i0 + k0 + b * kMergeThreads + (tid & 31);
+                const bool live = k0 + b * kMergeThreads + (tid & 31) <= r.nrows && gi < p.M;
+                end[b] = live ? __ldg(row_end + gi) : 0;
+                beg[b] = live ? __ldg(p.row_ptr + gi) : 0;
+            }
+#pragma unroll
+            for (int b = 0; b < SB; ++b) {
+                const int kw = k0 + b * kMergeThreads;  // the same for the whole warp
+                if (kw <= r.nrows) {
+                    const int k = kw + (tid & 31);
+                    if (k <= r.nrows) s.rowend[k] = (k < r.nrows) ? (end[b] - p.rp_base - r.j0) : INT_MAX;
+                    const unsigned bits = __ballot_sync(0xffffffffu, end[b] - beg[b] >= p.skip_len);
+                    if ((tid & 31) == 0) s.longbits[kw >> 5] = bits;
+                }
+            }
+        }
+        __syncthreads();
+        for (int k0 = tid; k0 < r.nnzt; k0 += kMergeThreads * SB) {
+            int c[SB];
+            float a[SB];
+            bool fetch[SB];
+#pragma unroll
+            for (int b = 0; b < SB; ++b) {
+                const int k = k0 + b * kMergeThreads;
+                fetch[b] = k < r.nnzt;
+                if (fetch[b]) {
+                    // the row that holds the first entry of this warp's run of 32
+                    const int run = k & ~31;
+                    int lo = 0, hi = r.nrows;
+                    while (lo < hi) {
+                        const int mid = (lo + hi) >> 1;
+                        if (s.rowend[mid] <= run) lo = mid + 1;
+                        else hi = mid;
+                    }
+                    if (s.is_long(lo) && s.rowend[lo] >= min(run + 32, r.nnzt)) {
+                        s.cv[k] = make_int2(0, 0);  // never read as data, but a batch may gather row 0 of B for it
+                        fetch[b] = false;
+                    }
+                }
+            }
+#pragma unroll
+            for (int b = 0; b < SB; ++b) {
+                if (fetch[b]) {
+                    const int k = k0 + b * kMergeThreads;
+                    c[b] = __ldcs(p.col_idx + r.j0 + k);
+                    a[b] = load_value<FMT>(p.values, r.j0 + k, p.value_scale);
+                }
+            }
+#pragma unroll
+            for (int b = 0; b < SB; ++b)
+                if (fetch[b]) s.cv[k0 + b * kMergeThreads] = make_int2(clamp_col(c[b]), __float_as_int(a[b]));
+        }
+    } else {
+        // row ends and entries are independent lists: both requested before either is stored
+        for (int k0 = tid; k0 <= r.nrows || k0 < r.nnzt; k0 += kMergeThreads * SB) {
+            int end[SB], c[SB];
+            float a[SB];
+#pragma unroll
+            for (int b = 0; b < SB; ++b) {
+                const int k = k0 + b * kMergeThreads;
+                if (k < r.nrows) end[b] = __ldg(row_end + r.i0 + k);
+                if (k < r.nnzt) {
+                    c[b] = __ldcs(p.col_idx + r.j0 + k);
+                    a[b] = load_value<FMT>(p.values, r.j0 + k, p.value_scale);
+                }
+            }
+#pragma unroll
+            for (int b = 0; b < SB; ++b) {
+                const int k = k0 + b * kMergeThreads;
+                if (k <= r.nrows) s.rowend[k] = (k < r.nrows) ? (end[b] - p.rp_base - r.j0) : INT_MAX;
+                if (k < r.nnzt) s.cv[k] = make_int2(clamp_col(c[b]), __float_as_int(a[b]));
+            }
+        }
     }
     __syncthreads();
 
@@ -188,6 +234,57 @@ __device__ __forceinline__ bool merge_tile_setup(const SpmmParams& p, Smem& s, T
     r.il1 = merge_search_local(dl1, s.rowend, r.nrows, r.nnzt);
     r.jl1 = dl1 - r.il1;
     return true;
+}
+
+// Step 5 for CTAs of many small lane groups (more than 32 of them): a tile inside a long row leaves
+// one partial sum per group, and one thread adding them all is the longest chain of the tile.  The
+// CTA's last warp does it: it finds the run of groups that stopped inside the open row 32 groups
+// per vote, cuts the run into 32 / (G * NV) contiguous chunks, every lane adds one chunk for one
+// column vector in group order, and the chunk sums are added in chunk order.  A fixed order, so the
+// carry is the same on every run.
+template <class Smem, int G, int NV, int VW>
+__device__ __forceinline__ void merge_carry_by_warp(const SpmmParams& p, Smem& s, const TileRange& r, int cb)
+{
+    constexpr int GROUPS = Smem::GROUPS;
+    constexpr int POS = G * NV;       // column vectors one group holds per pass
+    constexpr int CHUNKS = 32 / POS;
+    static_assert(GROUPS % 32 == 0 && POS <= 32 && 32 % POS == 0, "merge_carry_by_warp: lane groups must tile a warp");
+    const int wl = threadIdx.x & 31;
+
+    int gs = 0;
+    for (int base = GROUPS - 32; base >= 0; base -= 32) {
+        const unsigned open = __ballot_sync(0xffffffffu, s.tail_row[base + wl] == r.nrows);
+        const int lead = __clz((int)~open);  // groups at the top of these 32 that belong to the run
+        if (lead < 32) {
+            gs = base + 32 - lead;
+            break;
+        }
+    }
+    if (wl == 0 && cb == 0) p.carry_row[blockIdx.x] = (gs < GROUPS) ? (r.i0 + r.nrows) : -1;
+    if (gs >= GROUPS) return;
+
+    const int pos = wl % POS;
+    const int chunk = wl / POS;
+    const int per = (GROUPS - gs + CHUNKS - 1) / CHUNKS;
+    const int q0 = gs + chunk * per;
+    const int q1 = min(q0 + per, GROUPS);
+    Vec<VW> sum;
+    sum.zero();
+    if (q0 < q1) {
+        sum.load(s.tail_of(q0) + pos * VW);
+        for (int q = q0 + 1; q < q1; ++q) {
+            Vec<VW> t;
+            t.load(s.tail_of(q) + pos * VW);
+            sum.add(t);
+        }
+    }
+    Vec<VW> total = sum;  // chunk 0 is never empty
+    for (int c = 1; c < CHUNKS; ++c) {
+        const Vec<VW> t = sum.shuffle(c * POS + pos);
+        if (gs + c * per < GROUPS) total.add(t);
+    }
+    const int cv = cb + pos;
+    if (chunk == 0 && cv < p.ncolv) total.store(p.carry_val + (long long)blockIdx.x * p.carry_ld + (long long)cv * VW);
 }
 
 // Steps 4-5 for one column pass.  acc = the group's unfinished partial sum (valid when dirty),
@@ -233,7 +330,9 @@ __device__ __forceinline__ void merge_tile_finish(const SpmmParams& p, Smem& s, 
     }
 
     // ---- 5. the row this CTA leaves unfinished ------------------------------------------------
-    if (g == GROUPS - 1) {
+    if constexpr (GROUPS > 32) {
+        if (threadIdx.x >= kMergeThreads - 32) merge_carry_by_warp<Smem, G, NV, VW>(p, s, r, cb);
+    } else if (g == GROUPS - 1) {
         int gs = GROUPS;
         while (gs > 0 && s.tail_row[gs - 1] == r.nrows) --gs;
         if (lane == 0 && cb == 0) p.carry_row[blockIdx.x] = (gs < GROUPS) ? (r.i0 + r.nrows) : -1;

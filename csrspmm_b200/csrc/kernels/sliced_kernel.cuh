@@ -69,6 +69,7 @@ __global__ void __launch_bounds__(kSlicedThreads, MINB) spmm_sliced_kernel(const
     constexpr int GROUPS = kSlicedThreads / G;
     constexpr int ROWW = G * NV * VW;  // floats per ring slot
     constexpr int NB = D / 4;  // completion groups in flight
+    constexpr int SB = 4;      // (col, val) loads in flight per lane while a piece is staged
     static_assert(D % 4 == 0 && (D & (D - 1)) == 0, "ring depth must be a power of two and a multiple of 4");
     extern __shared__ __align__(16) unsigned char sliced_smem[];
     const cg::thread_block_tile<G> tile = cg::tiled_partition<G>(cg::this_thread_block());
@@ -96,13 +97,28 @@ __global__ void __launch_bounds__(kSlicedThreads, MINB) spmm_sliced_kernel(const
             off[k] = total;
             slot_of[k] = d.z;
         }
-        for (int j = rs + lane; j < re; j += G) {
-            int c = __ldcs(p.col_idx + j);
-            if ((unsigned)c >= (unsigned)p.Kd) {  // never fault on a bad index
-                c = min(max(c, 0), p.Kd - 1);
-                report_status(p, kStatusColClamped);
+        for (int j0 = rs + lane; j0 < re; j0 += G * SB) {  // SB loads in flight per lane, then the stores
+            int c[SB];
+            float a[SB];
+#pragma unroll
+            for (int b = 0; b < SB; ++b) {
+                const int j = j0 + b * G;
+                if (j < re) {
+                    c[b] = __ldcs(p.col_idx + j);
+                    a[b] = load_value<FMT>(p.values, j, p.value_scale);
+                }
             }
-            cvbuf[total + (j - rs)] = make_int2(c, __float_as_int(load_value<FMT>(p.values, j, p.value_scale)));
+#pragma unroll
+            for (int b = 0; b < SB; ++b) {
+                const int j = j0 + b * G;
+                if (j < re) {
+                    if ((unsigned)c[b] >= (unsigned)p.Kd) {  // never fault on a bad index
+                        c[b] = min(max(c[b], 0), p.Kd - 1);
+                        report_status(p, kStatusColClamped);
+                    }
+                    cvbuf[total + (j - rs)] = make_int2(c[b], __float_as_int(a[b]));
+                }
+            }
         }
         total += re - rs;
         ++np;

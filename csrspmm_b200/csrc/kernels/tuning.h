@@ -95,6 +95,10 @@
 #endif
 
 // threads per CTA of the merge-path kernels (merge, bulk-copy): lane groups per CTA = this / G
+// merge-path tile staging: global loads in flight per thread before the stores to shared memory
+#ifndef CSRSPMM_TUNE_MERGE_STAGE_BATCH
+#define CSRSPMM_TUNE_MERGE_STAGE_BATCH 6
+#endif
 #ifndef CSRSPMM_TUNE_MERGE_THREADS
 #define CSRSPMM_TUNE_MERGE_THREADS 256
 #endif
