@@ -504,12 +504,18 @@ def main(argv=None):
     # library decides by itself whether this matrix and this width of B are worth one
     schedule, sched_info = None, None
     if ns.kernel == "auto" and not ns.no_schedule and my_rows > 0:
-        torch.cuda.synchronize()
-        t0 = time.perf_counter()
-        schedule = ops.Schedule(t["row_ptr"], t["col_idx"], Kd, Nd, threshold=ns.sched_threshold,
-                                slab_rows=(ns.sched_slab_mib << 20) // (Nd * 4), piece_nnz=ns.sched_piece)
-        torch.cuda.synchronize()
-        sched_info = dict(schedule.info(), build_wall_ms=(time.perf_counter() - t0) * 1e3)
+        def build_schedule():
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            sch = ops.Schedule(t["row_ptr"], t["col_idx"], Kd, Nd, threshold=ns.sched_threshold,
+                               slab_rows=(ns.sched_slab_mib << 20) // (Nd * 4), piece_nnz=ns.sched_piece)
+            torch.cuda.synchronize()
+            return sch, (time.perf_counter() - t0) * 1e3
+        # the first build of a process also loads the library's kernels; the second is what a schedule costs
+        schedule, first_ms = build_schedule()
+        schedule.close()
+        schedule, wall_ms = build_schedule()
+        sched_info = dict(schedule.info(), build_wall_ms=wall_ms, first_build_in_process_wall_ms=first_ms)
         if schedule.active:
             chosen, launches_per_step = "scheduled", 4
         else:

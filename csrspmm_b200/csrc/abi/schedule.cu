@@ -12,6 +12,7 @@
 // pass writes the slab-major piece list.  Two small host reads size the arrays in between.
 #include <cuda_runtime.h>
 
+#include <algorithm>
 #include <chrono>
 #include <cstdlib>
 #include <cstring>
@@ -44,6 +45,8 @@ struct csrspmm_b200_schedule {
 namespace {
 
 constexpr uint32_t kScheduleMagic = 0x53434844u;  // "SCHD"
+constexpr int kSlicedCtasPerSm = 3;  // more than fit is harmless: a late CTA finds the list used up
+constexpr size_t kTicketBytes = 256;  // the ticket counter of the pieces kernel, in the call's scratch
 
 #define CUDA_TRY(expr)                                                                      \
     do {                                                                                    \
@@ -69,9 +72,10 @@ int env_int(const char* name)
 // 32 / 48 / 64 MiB at 2048, against 40.5 ms without a schedule.
 constexpr size_t kSlabBytes = (size_t)64 << 20;
 // A row is scheduled when it has this many entries per slab on average: each piece costs a slot
-// written and read back (one row of Nd floats each way), so a few entries per piece buy nothing
-// (config 5: thresholds of 8 / 16 / 32 / 64 entries per 32 MiB slab gave 40.2 / 38.9 / 38.9 / 39.6 ms).
-constexpr int kMinEntriesPerSlab = 16;
+// written and read back (one row of Nd floats each way), so a few entries per piece buy nothing.
+// Config 5, 128 slabs of 64 MiB, persistent pieces kernel: 2 / 3 / 4 / 6 / 8 / 12 / 16 entries per
+// slab gave 38.1 / 37.1 / 36.9 / 36.8 / 36.8 / 37.2 / 37.4 ms.
+constexpr int kMinEntriesPerSlab = 8;
 constexpr int kDefaultPiece = 64;
 // Below this many bytes per row of B the library schedules nothing unless a threshold is given:
 // with narrow rows the time of a product is set by its short rows (a chain of dependent loads per
@@ -217,7 +221,7 @@ size_t scheduled_workspace_bytes(const csrspmm_b200_args* a)
     Plan plan;
     if (scheduled_plan(a, &plan) != CSRSPMM_B200_OK) return 0;
     const size_t slot_ld = ((size_t)a->Nd + 3) / 4 * 4;
-    return plan.workspace_bytes + align256((size_t)a->schedule->num_pieces * slot_ld * sizeof(float));
+    return plan.workspace_bytes + kTicketBytes + align256((size_t)a->schedule->num_pieces * slot_ld * sizeof(float));
 }
 
 int enqueue_scheduled(const csrspmm_b200_args* a, cudaStream_t st)
@@ -247,7 +251,7 @@ int enqueue_scheduled(const csrspmm_b200_args* a, cudaStream_t st)
     int status = scheduled_plan(a, &plan);
     if (status != CSRSPMM_B200_OK) return status;
     const size_t slot_ld = ((size_t)a->Nd + 3) / 4 * 4;
-    const size_t need = plan.workspace_bytes + align256((size_t)s->num_pieces * slot_ld * sizeof(float));
+    const size_t need = plan.workspace_bytes + kTicketBytes + align256((size_t)s->num_pieces * slot_ld * sizeof(float));
 
     void* ws = nullptr;
     bool ws_owned = false;
@@ -274,20 +278,27 @@ int enqueue_scheduled(const csrspmm_b200_args* a, cudaStream_t st)
     q.num_pieces = (int)s->num_pieces;
     q.pieces_per_group = CSRSPMM_TUNE_SLICED_PIECES_PER_GROUP;
     q.piece_cap = s->piece_nnz;
-    q.slots = reinterpret_cast<float*>(static_cast<char*>(ws) + plan.workspace_bytes);
+    q.tickets = reinterpret_cast<unsigned*>(static_cast<char*>(ws) + plan.workspace_bytes);
+    q.slots = reinterpret_cast<float*>(static_cast<char*>(ws) + plan.workspace_bytes + kTicketBytes);
     q.slot_ld = (long long)slot_ld;
     q.long_rows = s->long_rows;
     q.num_long_rows = s->num_long;
     q.evict_last = CSRSPMM_TUNE_SLICED_EVICT_LAST;
 
     const bool e2m1 = a->value_format == CSRSPMM_B200_VALUES_E2M1;
+    // a persistent grid: every warp draws runs of pieces until the list is used up
     const long long per_cta = (long long)(kSlicedThreads / kPieceShapes[plan.shape].G) * q.pieces_per_group;
-    const unsigned grid_pieces = (unsigned)((s->num_pieces + per_cta - 1) / per_cta);
-    cudaError_t err;
-    if (plan.VW == 4) {
-        err = e2m1 ? dispatch_sliced<4, kValuesE2M1>(p, q, plan, grid_pieces, st) : dispatch_sliced<4, kValuesF32>(p, q, plan, grid_pieces, st);
-    } else {
-        err = e2m1 ? dispatch_sliced<1, kValuesE2M1>(p, q, plan, grid_pieces, st) : dispatch_sliced<1, kValuesF32>(p, q, plan, grid_pieces, st);
+    const long long ctas_of_work = (s->num_pieces + per_cta - 1) / per_cta + 1;
+    int sms = 148;
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+    const unsigned grid_pieces = (unsigned)std::min<long long>(ctas_of_work, (long long)sms * kSlicedCtasPerSm);
+    cudaError_t err = cudaMemsetAsync(q.tickets, 0, kTicketBytes, st);
+    if (err == cudaSuccess) {
+        if (plan.VW == 4) {
+            err = e2m1 ? dispatch_sliced<4, kValuesE2M1>(p, q, plan, grid_pieces, st) : dispatch_sliced<4, kValuesF32>(p, q, plan, grid_pieces, st);
+        } else {
+            err = e2m1 ? dispatch_sliced<1, kValuesE2M1>(p, q, plan, grid_pieces, st) : dispatch_sliced<1, kValuesF32>(p, q, plan, grid_pieces, st);
+        }
     }
     if (err == cudaSuccess) {
         const long long threads = (long long)s->num_long * plan.ncolv;

@@ -9,13 +9,13 @@
 // boundaries, cuts every part again into pieces of bounded length and lists the pieces slab by
 // slab.  Here:
 //
-//   spmm_sliced_kernel   one lane group per piece, pieces taken in list order (CTA c owns pieces
-//                        [c*ipc, (c+1)*ipc), its groups take them round-robin): a sequential fp32
-//                        sum over the piece's entries, U B-row loads in flight per lane, written
-//                        raw (no alpha/beta) to the piece's own slot of scratch.  The descriptor of
-//                        the group's next piece and that piece's first (col, val) chunk are
-//                        requested while the current piece is summed, so a piece costs one
-//                        dependent round trip per U entries and nothing to start.
+//   spmm_sliced_kernel   a persistent grid; every warp draws runs of consecutive pieces from the list
+//                        (one ticket counter, the next ticket requested while the current run is
+//                        summed), its lane groups sum a few pieces each: a sequential fp32 sum over
+//                        the piece's entries, the rows of B pipelined through a ring in shared
+//                        memory, written raw (no alpha/beta) to the piece's own slot of scratch.
+//                        Drawing in list order keeps every SM on the same one or two slabs at any
+//                        time; which warp sums a piece does not change the sum.
 //   spmm_slot_reduce_kernel   one thread per long row and column vector: the row's slots added in stored order,
 //                        then C[row] = alpha * sum + beta * C[row].  No atomics anywhere, so the
 //                        result is the same on every run; a row that fits one piece is the
@@ -46,6 +46,7 @@ struct SlicedParams {
     const int4* long_rows; // {row, first slot, slot count, unused}
     int num_long_rows;
     int evict_last;        // B loads carry an evict_last policy (the slab should outlive the streams)
+    unsigned* tickets;     // one counter, zero at launch: runs of pieces handed out in list order
 };
 
 // Shared memory of one CTA of spmm_sliced_kernel, in bytes: the ring of gathered B rows, the staged
@@ -56,13 +57,13 @@ __host__ __device__ constexpr size_t sliced_smem_bytes(int G, int NV, int VW, in
     return groups * D * (size_t)(G * NV * VW) * 4 + groups * (size_t)ppg * cap * 8 + groups * (size_t)(2 * ppg + 2) * 4;
 }
 
-// One lane group sums `pieces_per_group` consecutive pieces.  It first copies their (col, val) pairs
-// to shared memory (coalesced, all requests in flight together), then runs one pipeline over all of
-// them: the rows of B for entries f + D .. f + D + 3 are requested (asynchronous copies into the
-// group's ring, each lane its own 16 bytes of a row, so no lane ever reads what another lane copied)
-// while entries f .. f + 3 are multiplied.  D rows per group stay in flight whatever the piece
-// boundaries are, and a slow row (a miss in L2) delays the group only when it reaches the head of
-// the ring.
+// A warp takes a run of (32 / G) * pieces_per_group consecutive pieces; each of its lane groups sums
+// `pieces_per_group` of them.  The group first copies their (col, val) pairs to shared memory
+// (coalesced, several requests in flight), then runs one pipeline over all of them: the rows of B
+// for entries f + D .. f + D + 3 are requested (asynchronous copies into the group's ring, each
+// lane its own 16 bytes of a row, so no lane ever reads what another lane copied) while entries
+// f .. f + 3 are multiplied.  D rows per group stay in flight whatever the piece boundaries are, and
+// a slow row (a miss in L2) delays the group only when it reaches the head of the ring.
 template <int G, int NV, int VW, int D, int FMT, bool FULL, int MINB>
 __global__ void __launch_bounds__(kSlicedThreads, MINB) spmm_sliced_kernel(const SpmmParams p, const SlicedParams q)
 {
@@ -75,8 +76,10 @@ __global__ void __launch_bounds__(kSlicedThreads, MINB) spmm_sliced_kernel(const
     const cg::thread_block_tile<G> tile = cg::tiled_partition<G>(cg::this_thread_block());
     const int lane = tile.thread_rank();
     const int g = threadIdx.x / G;
+    const int wl = threadIdx.x & 31;
     const int ppg = q.pieces_per_group;
     const int cap = ppg * q.piece_cap;
+    const int run = (32 / G) * ppg;  // pieces per ticket
 
     float* const ring = reinterpret_cast<float*>(sliced_smem) + (size_t)g * D * ROWW;
     int2* const cvbuf = reinterpret_cast<int2*>(sliced_smem + (size_t)GROUPS * D * ROWW * 4) + (size_t)g * cap;
@@ -85,143 +88,164 @@ __global__ void __launch_bounds__(kSlicedThreads, MINB) spmm_sliced_kernel(const
     int* const off = tab;             // off[k] = first flat position of piece k, off[np] = total
     int* const slot_of = tab + ppg + 1;
 
-    // ---- the group's pieces and their (col, val) pairs ------------------------------------------------
-    const long long it0 = ((long long)blockIdx.x * GROUPS + g) * ppg;
-    int total = 0, np = 0;
-    for (int k = 0; k < ppg; ++k) {
-        if (it0 + k >= q.num_pieces) break;
-        const int4 d = __ldg(q.pieces + it0 + k);
-        const int rs = min(max(d.x, 0), p.nnz);
-        const int re = min(max(d.y, rs), min(p.nnz, rs + q.piece_cap));
-        if (lane == 0) {
-            off[k] = total;
-            slot_of[k] = d.z;
-        }
-        for (int j0 = rs + lane; j0 < re; j0 += G * SB) {  // SB loads in flight per lane, then the stores
-            int c[SB];
-            float a[SB];
-#pragma unroll
-            for (int b = 0; b < SB; ++b) {
-                const int j = j0 + b * G;
-                if (j < re) {
-                    c[b] = __ldcs(p.col_idx + j);
-                    a[b] = load_value<FMT>(p.values, j, p.value_scale);
-                }
-            }
-#pragma unroll
-            for (int b = 0; b < SB; ++b) {
-                const int j = j0 + b * G;
-                if (j < re) {
-                    if ((unsigned)c[b] >= (unsigned)p.Kd) {  // never fault on a bad index
-                        c[b] = min(max(c[b], 0), p.Kd - 1);
-                        report_status(p, kStatusColClamped);
-                    }
-                    cvbuf[total + (j - rs)] = make_int2(c[b], __float_as_int(a[b]));
-                }
-            }
-        }
-        total += re - rs;
-        ++np;
-    }
-    if (lane == 0) off[np] = total;
-    tile.sync();
-    if (np == 0) return;
-
     const char* const b_lane = reinterpret_cast<const char*>(p.B) + (size_t)lane * (VW * 4);
     const unsigned ring_lane = smem_addr(ring) + (unsigned)lane * (VW * 4);
     unsigned long long policy = 0;
     if (q.evict_last) asm("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(policy));
     const bool hinted = q.evict_last != 0;
 
-    for (int cb = 0; cb < p.ncolv; cb += G * NV) {
-        const char* const b_pass = b_lane + (size_t)cb * (VW * 4);
-        bool col_ok[NV];
-#pragma unroll
-        for (int v = 0; v < NV; ++v) col_ok[v] = FULL || (cb + lane + v * G < p.ncolv);
+    // ---- runs of pieces, handed out in list order ---------------------------------------------------------
+    auto fetch = [&]() -> unsigned { return wl == 0 ? atomicAdd(q.tickets, 1u) : 0u; };
+    // ticket -> first piece and end of the run (the same in every lane); first < 0: the list is used up
+    auto resolve = [&](unsigned ticket, int& first, int& last) {
+        const unsigned t = __shfl_sync(0xffffffffu, ticket, 0);
+        if ((long long)t * run < (long long)q.num_pieces) {
+            first = (int)t * run;
+            last = min(first + run, q.num_pieces);
+        } else {
+            first = -1;
+            last = 0;
+        }
+    };
 
-        auto issue = [&](int f) {
-            const char* brow = b_pass + (unsigned long long)(unsigned)cvbuf[f].x * p.ldb_bytes;
-            const unsigned dst = ring_lane + (unsigned)(f & (D - 1)) * (ROWW * 4);
-#pragma unroll
-            for (int v = 0; v < NV; ++v) {
-                if (col_ok[v]) {
-                    if (hinted) async_copy_vec_hint<VW>(dst + v * (G * VW * 4), brow + v * (G * VW * 4), policy);
-                    else async_copy_vec<VW>(dst + v * (G * VW * 4), brow + v * (G * VW * 4));
-                }
-            }
-        };
-        auto store_piece = [&](int k, const Vec<VW> (&acc)[NV]) {
-            float* slot = q.slots + (long long)slot_of[k] * q.slot_ld;
-#pragma unroll
-            for (int v = 0; v < NV; ++v) {
-                const int cv = cb + lane + v * G;
-                if (FULL || cv < p.ncolv) {
-                    if (CSRSPMM_TUNE_SLICED_STREAM_SLOTS) acc[v].store_streaming(slot + (long long)cv * VW);
-                    else acc[v].store(slot + (long long)cv * VW);
-                }
-            }
-        };
+    int run_first, run_last;
+    resolve(fetch(), run_first, run_last);
+    while (run_first >= 0) {
+        const unsigned next_ticket = fetch();  // on its way while this run is summed; looked at only after it
 
-        auto multiply = [&](int f, Vec<VW> (&acc)[NV]) {
-            const float a = __int_as_float(cvbuf[f].y);
-            const float* src = ring + (size_t)(f & (D - 1)) * ROWW + lane * VW;
+        // ---- the group's pieces and their (col, val) pairs ------------------------------------------------
+        const int it0 = run_first + (wl / G) * ppg;
+        int total = 0, np = 0;
+        for (int k = 0; k < ppg; ++k) {
+            if (it0 + k >= run_last) break;
+            const int4 d = __ldg(q.pieces + it0 + k);
+            const int rs = min(max(d.x, 0), p.nnz);
+            const int re = min(max(d.y, rs), min(p.nnz, rs + q.piece_cap));
+            if (lane == 0) {
+                off[k] = total;
+                slot_of[k] = d.z;
+            }
+            for (int j0 = rs + lane; j0 < re; j0 += G * SB) {  // SB loads in flight per lane, then the stores
+                int c[SB];
+                float a[SB];
 #pragma unroll
-            for (int v = 0; v < NV; ++v) {
-                if (col_ok[v]) {
-                    Vec<VW> b;
-                    b.load(src + v * (G * VW));
-                    acc[v].fma(a, b);
+                for (int b = 0; b < SB; ++b) {
+                    const int j = j0 + b * G;
+                    if (j < re) {
+                        c[b] = __ldcs(p.col_idx + j);
+                        a[b] = load_value<FMT>(p.values, j, p.value_scale);
+                    }
                 }
-            }
-        };
-        // requests go out four at a time, one completion group per four: the group of entries
-        // f .. f+3 is always the NB-th youngest when they are multiplied
-        auto request_four = [&](int f) {
-            if (f + 4 <= total) {
 #pragma unroll
-                for (int u = 0; u < 4; ++u) issue(f + u);
-            } else {
-#pragma unroll
-                for (int u = 0; u < 4; ++u)
-                    if (f + u < total) issue(f + u);
-            }
-            async_commit();
-        };
-#pragma unroll
-        for (int b = 0; b < NB; ++b) request_four(b * 4);
-        Vec<VW> acc[NV];
-#pragma unroll
-        for (int v = 0; v < NV; ++v) acc[v].zero();
-        int k = 0;
-        int next_off = off[1];
-        for (int f = 0; f < total; f += 4) {
-            async_wait<NB - 1>();
-            if (f + 4 <= next_off) {  // inside one piece (f < next_off <= total)
-#pragma unroll
-                for (int u = 0; u < 4; ++u) multiply(f + u, acc);
-            } else {
-#pragma unroll
-                for (int u = 0; u < 4; ++u) {
-                    if (f + u < total) {
-                        while (f + u >= next_off) {  // an empty piece writes zeros
-                            store_piece(k, acc);
-#pragma unroll
-                            for (int v = 0; v < NV; ++v) acc[v].zero();
-                            ++k;
-                            next_off = off[k + 1];
+                for (int b = 0; b < SB; ++b) {
+                    const int j = j0 + b * G;
+                    if (j < re) {
+                        if ((unsigned)c[b] >= (unsigned)p.Kd) {  // never fault on a bad index
+                            c[b] = min(max(c[b], 0), p.Kd - 1);
+                            report_status(p, kStatusColClamped);
                         }
-                        multiply(f + u, acc);
+                        cvbuf[total + (j - rs)] = make_int2(c[b], __float_as_int(a[b]));
                     }
                 }
             }
-            request_four(f + D);
+            total += re - rs;
+            ++np;
         }
-        for (; k < np; ++k) {  // the last piece, and empty ones after it
-            store_piece(k, acc);
+        if (lane == 0) off[np] = total;
+        tile.sync();
+
+        for (int cb = 0; np > 0 && cb < p.ncolv; cb += G * NV) {
+            const char* const b_pass = b_lane + (size_t)cb * (VW * 4);
+            bool col_ok[NV];
+#pragma unroll
+            for (int v = 0; v < NV; ++v) col_ok[v] = FULL || (cb + lane + v * G < p.ncolv);
+
+            auto issue = [&](int f) {
+                const char* brow = b_pass + (unsigned long long)(unsigned)cvbuf[f].x * p.ldb_bytes;
+                const unsigned dst = ring_lane + (unsigned)(f & (D - 1)) * (ROWW * 4);
+#pragma unroll
+                for (int v = 0; v < NV; ++v) {
+                    if (col_ok[v]) {
+                        if (hinted) async_copy_vec_hint<VW>(dst + v * (G * VW * 4), brow + v * (G * VW * 4), policy);
+                        else async_copy_vec<VW>(dst + v * (G * VW * 4), brow + v * (G * VW * 4));
+                    }
+                }
+            };
+            auto store_piece = [&](int k, const Vec<VW> (&acc)[NV]) {
+                float* slot = q.slots + (long long)slot_of[k] * q.slot_ld;
+#pragma unroll
+                for (int v = 0; v < NV; ++v) {
+                    const int cv = cb + lane + v * G;
+                    if (FULL || cv < p.ncolv) {
+                        if (CSRSPMM_TUNE_SLICED_STREAM_SLOTS) acc[v].store_streaming(slot + (long long)cv * VW);
+                        else acc[v].store(slot + (long long)cv * VW);
+                    }
+                }
+            };
+
+            auto multiply = [&](int f, Vec<VW> (&acc)[NV]) {
+                const float a = __int_as_float(cvbuf[f].y);
+                const float* src = ring + (size_t)(f & (D - 1)) * ROWW + lane * VW;
+#pragma unroll
+                for (int v = 0; v < NV; ++v) {
+                    if (col_ok[v]) {
+                        Vec<VW> b;
+                        b.load(src + v * (G * VW));
+                        acc[v].fma(a, b);
+                    }
+                }
+            };
+            // requests go out four at a time, one completion group per four: the group of entries
+            // f .. f+3 is always the NB-th youngest when they are multiplied
+            auto request_four = [&](int f) {
+                if (f + 4 <= total) {
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) issue(f + u);
+                } else {
+#pragma unroll
+                    for (int u = 0; u < 4; ++u)
+                        if (f + u < total) issue(f + u);
+                }
+                async_commit();
+            };
+#pragma unroll
+            for (int b = 0; b < NB; ++b) request_four(b * 4);
+            Vec<VW> acc[NV];
 #pragma unroll
             for (int v = 0; v < NV; ++v) acc[v].zero();
+            int k = 0;
+            int next_off = off[1];
+            for (int f = 0; f < total; f += 4) {
+                async_wait<NB - 1>();
+                if (f + 4 <= next_off) {  // inside one piece (f < next_off <= total)
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) multiply(f + u, acc);
+                } else {
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        if (f + u < total) {
+                            while (f + u >= next_off) {  // an empty piece writes zeros
+                                store_piece(k, acc);
+#pragma unroll
+                                for (int v = 0; v < NV; ++v) acc[v].zero();
+                                ++k;
+                                next_off = off[k + 1];
+                            }
+                            multiply(f + u, acc);
+                        }
+                    }
+                }
+                request_four(f + D);
+            }
+            for (; k < np; ++k) {  // the last piece, and empty ones after it
+                store_piece(k, acc);
+#pragma unroll
+                for (int v = 0; v < NV; ++v) acc[v].zero();
+            }
+            async_wait<0>();
         }
-        async_wait<0>();
+        tile.sync();  // the group's tables and ring are rewritten for the next run
+        resolve(next_ticket, run_first, run_last);
     }
 }
 

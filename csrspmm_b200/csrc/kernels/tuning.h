@@ -26,7 +26,7 @@
 
 // scheduled pieces (sliced_kernel.cuh): consecutive pieces per lane group
 #ifndef CSRSPMM_TUNE_SLICED_PIECES_PER_GROUP
-#define CSRSPMM_TUNE_SLICED_PIECES_PER_GROUP 2
+#define CSRSPMM_TUNE_SLICED_PIECES_PER_GROUP 1
 #endif
 // scheduled pieces load B with an evict_last policy (1) or plainly (0)
 #ifndef CSRSPMM_TUNE_SLICED_EVICT_LAST

@@ -240,7 +240,7 @@ def test_cfg5_xl_eighth_size_under_the_librarys_own_schedule(cuda_lib):
     rp_h = p.row_ptr.cpu().numpy()
     s = ops.Schedule(p.row_ptr, p.col_idx, p.Kd, p.Nd)
     info = s.info()
-    assert s.active and info["num_slabs"] == 16 and info["long_row_threshold"] == 256, info
+    assert s.active and info["num_slabs"] == 16 and info["long_row_threshold"] == 128, info  # 8 entries per slab
     Cd = ops.spmm(p.row_ptr, p.col_idx, p.values, p.B, sync=True, schedule=s)
     rate = _check_sampled_rows(rp_h, p.col_idx, p.values, p.B, Cd, _sample(rp_h, np.random.default_rng(1), 4000, 32))
     assert rate > 0.999
@@ -248,3 +248,16 @@ def test_cfg5_xl_eighth_size_under_the_librarys_own_schedule(cuda_lib):
     plain = ops.spmm(p.row_ptr, p.col_idx, p.values, p.B, kernel="merge", sync=True)
     short = torch.from_numpy(np.diff(rp_h) < info["long_row_threshold"]).cuda()
     assert torch.equal(Cd[short], plain[short])
+
+
+def test_results_do_not_depend_on_which_warp_sums_a_piece(cuda_lib):
+    """The pieces are drawn from a ticket counter by whichever warp is free: the draw changes from run to run, no
+    sum may."""
+    p = skewed(3000, 4096, 64, seed=11, mean=24.0)
+    rp, ci, va, B = dev(p.row_ptr), dev(p.col_idx), dev(p.values), dev(p.B)
+    sched = ops.Schedule(rp, ci, p.Kd, p.Nd, threshold=32, slab_rows=128, piece_nnz=16)
+    assert sched.active
+    first = ops.spmm(rp, ci, va, B, schedule=sched, sync=True)
+    for _ in range(5):
+        assert torch.equal(first, ops.spmm(rp, ci, va, B, schedule=sched, sync=True))
+    check(first.cpu().numpy(), p)
