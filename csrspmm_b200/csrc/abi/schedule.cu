@@ -85,9 +85,10 @@ constexpr int kDefaultPiece = 64;
 constexpr size_t kMinRowBytesForAuto = 1024;
 // ... and nothing when the scheduled rows together name each row of B fewer than this many times: what the
 // pieces save is the re-use of a slab's rows while it sits in L2, and a row block of a matrix cut across N
-// GPUs has 1/N of the re-use (config 5: 6.4 / 3.2 / 1.6 / 0.8 entries per row of B on 1 / 2 / 4 / 8 GPUs;
-// 40.6 -> 38.3 ms and 20.4 -> 19.3 ms at 1 and 2 GPUs, 10.2 -> 10.1 ms at 4).
-constexpr double kMinReuseForAuto = 2.0;
+// GPUs has 1/N of the re-use (config 5: 8.1 / 4.0 / 2.0 / 1.0 entries per row of B on 1 / 2 / 4 / 8 GPUs;
+// 40.5 -> 36.7 ms, 20.3 -> 18.7 ms and 10.2 -> 9.75 ms at 1, 2 and 4 GPUs).  At one use per row of B every
+// row is fetched from HBM once either way and the slots come on top.
+constexpr double kMinReuseForAuto = 1.5;
 
 bool valid(const csrspmm_b200_schedule* s) { return s != nullptr && s->magic == kScheduleMagic; }
 

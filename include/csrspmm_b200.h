@@ -219,7 +219,7 @@ int csrspmm_b200_select_kernel(const csrspmm_b200_args* args);
  * Left to itself (no threshold in the options) the library schedules nothing -- the schedule comes back
  * empty and products run as without one -- when it would not pay: B fits one slab, rows of B under 1 KB
  * (there the short rows, not the bytes, set the time), or scheduled rows that together name each row of B
- * fewer than twice (no re-use to win; typical of a row block of a matrix cut across many GPUs).
+ * fewer than 1.5 times (no re-use to win; typical of a row block of a matrix cut across many GPUs).
  * The schedule holds device memory (csrspmm_b200_schedule_info.device_bytes) on the device that
  * was current at creation and must be used there.  It describes the sparsity pattern only: keep it
  * as long as row_ptr and col_idx are unchanged (values, B, C, alpha, beta and Nd may change; Nd
