@@ -77,6 +77,7 @@ constexpr size_t kSlabBytes = (size_t)64 << 20;
 // slab gave 38.1 / 37.1 / 36.9 / 36.8 / 36.8 / 37.2 / 37.4 ms.
 constexpr int kMinEntriesPerSlab = 8;
 constexpr int kDefaultPiece = 64;
+constexpr int kMaxPiece = 512;
 // Below this many bytes per row of B the library schedules nothing unless a threshold is given:
 // with narrow rows the time of a product is set by its short rows (a chain of dependent loads per
 // row that the merge-path kernel hides behind the long rows' streaming gather), and taking the long
@@ -366,6 +367,7 @@ int csrspmm_b200_schedule_create(const csrspmm_b200_args* a, const csrspmm_b200_
     if (threshold <= 0) threshold = env_int("CSRSPMM_SCHED_THRESHOLD");
     if (piece <= 0) piece = env_int("CSRSPMM_SCHED_PIECE");
     if (piece <= 0) piece = kDefaultPiece;
+    if (piece > kMaxPiece) piece = kMaxPiece;  // a lane group stages a whole piece in shared memory
     const size_t row_bytes = (size_t)(a->ldb > 0 ? a->ldb : 1) * 4;
     if (slab_rows <= 0) {
         size_t slab = kSlabBytes;

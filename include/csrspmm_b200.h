@@ -235,7 +235,7 @@ typedef struct csrspmm_b200_schedule_options {
     uint32_t struct_size;       /* sizeof(csrspmm_b200_schedule_options) */
     int32_t long_row_threshold; /* rows of this many entries or more are scheduled; 0 = choose */
     int32_t slab_rows;          /* rows of B per slab; 0 = choose (about 32 MiB of B) */
-    int32_t piece_nnz;          /* longest piece one lane group accumulates; 0 = choose */
+    int32_t piece_nnz;          /* longest piece one lane group accumulates; 0 = choose, at most 512 */
 } csrspmm_b200_schedule_options;
 
 typedef struct csrspmm_b200_schedule_info {

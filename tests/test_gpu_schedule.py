@@ -261,3 +261,23 @@ def test_results_do_not_depend_on_which_warp_sums_a_piece(cuda_lib):
     for _ in range(5):
         assert torch.equal(first, ops.spmm(rp, ci, va, B, schedule=sched, sync=True))
     check(first.cpu().numpy(), p)
+
+
+@pytest.mark.parametrize("seed", range(8))
+def test_random_schedules_match_the_oracle(cuda_lib, seed):
+    """Random sizes, widths and schedule parameters (few pieces, many pieces, more pieces than the persistent
+    grid has warps, pieces of one entry): every combination against the fp64 oracle and against itself."""
+    rng = np.random.default_rng(100 + seed)
+    M = int(rng.integers(50, 6000))
+    Kd = int(rng.integers(600, 9000))
+    Nd = int(rng.choice([1, 4, 12, 32, 64, 100, 128, 256, 516]))
+    p = skewed(M, Kd, Nd, seed=200 + seed, mean=float(rng.uniform(4, 40)), cap=Kd)
+    threshold = int(rng.choice([2, 8, 33, 200]))
+    slab_rows = int(rng.choice([256, 300, 1024, 4096]))
+    piece = int(rng.choice([1, 3, 16, 64, 500]))
+    rp, ci = dev(p.row_ptr), dev(p.col_idx)
+    sched = ops.Schedule(rp, ci, p.Kd, p.Nd, threshold=threshold, slab_rows=slab_rows, piece_nnz=piece)
+    C0 = rng.standard_normal((p.M, p.Nd), dtype=np.float32)
+    got = run(p, sched if sched.active else None, C0=C0, alpha=0.75, beta=-0.5)
+    check(got, p, C0=C0, alpha=0.75, beta=-0.5)
+    assert np.array_equal(got, run(p, sched if sched.active else None, C0=C0, alpha=0.75, beta=-0.5))
