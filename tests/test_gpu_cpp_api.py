@@ -39,3 +39,23 @@ def test_reference_test_program_passes_unchanged(cuda_lib, algo):
 def test_reference_benchmark_program_runs_unchanged(cuda_lib):
     code, out = _run([REF_BENCH, "-M", 1024, "-N", 1024, "-K", 128, "-s", 0.95, "-algo", "WarpPerRowFp4"])
     assert code == 0 and "GFLOPS" in out, out[-2000:]
+
+
+def test_l2_partition_probe_gives_a_clean_picture(cuda_lib):
+    """The probe behind the design notes on the two L2 partitions: on a two-die GPU the SMs fall into two groups
+    (every line splits them the same way or the opposite way) and a far line, once read, is as near as a near
+    one; on any other GPU the probe says so.  Either answer passes; a probe that cannot tell does not."""
+    import json
+    exe = ROOT / "tests" / "cpp" / "_bin" / "l2_partition_probe"
+    assert exe.exists(), "tests/cpp/_bin/l2_partition_probe not built (python -m csrspmm_b200.build)"
+    code, out = _run([exe])
+    assert code == 0, out[-2000:]
+    got = json.loads(out.strip().splitlines()[-1])
+    assert got["reporting"] == got["sms"], got
+    if got["two_partitions"]:
+        assert sum(got["group_sizes"]) == got["sms"] and min(got["group_sizes"]) * 4 >= got["sms"], got
+        assert got["atomic_cycles_far"] > 1.5 * got["atomic_cycles_near"], got
+        assert got["load_cycles_far_home"] < 1.25 * got["load_cycles_near_home"], got  # the far lines were copied near
+        assert 0 < got["lines_split_the_opposite_way"] < got["lines"], got
+    else:
+        assert got["group_sizes"] == [0, 0], got
