@@ -95,7 +95,7 @@ int main()
     std::vector<int> seen;
     for (int s = 0; s < kMaxSms; ++s)
         if (hc[(size_t)s]) seen.push_back(s);
-    bool two = (int)seen.size() == sms;
+    bool two = (int)seen.size() * 10 >= sms * 9;  // an SM that got no CTA of the probe is left out
     std::vector<int> group(seen.size(), 0);  // 1: near to line 0
     double near_a = 0, far_a = 0, near_l = 0, far_l = 0;
     long long near_n = 0, far_n = 0;
