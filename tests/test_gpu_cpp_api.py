@@ -55,7 +55,7 @@ def test_l2_partition_probe_gives_a_clean_picture(cuda_lib):
     if got["two_partitions"]:
         assert sum(got["group_sizes"]) == got["reporting"] and min(got["group_sizes"]) * 4 >= got["sms"], got
         assert got["atomic_cycles_far"] > 1.5 * got["atomic_cycles_near"], got
-        assert got["load_cycles_far_home"] < 1.25 * got["load_cycles_near_home"], got  # the far lines were copied near
+        assert got["load_cycles_far_home"] < 0.75 * got["atomic_cycles_far"], got  # the far lines were copied near
         assert 0 < got["lines_split_the_opposite_way"] < got["lines"], got
     else:
         assert got["group_sizes"] == [0, 0], got
