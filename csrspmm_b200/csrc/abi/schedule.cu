@@ -78,11 +78,12 @@ constexpr size_t kSlabBytes = (size_t)64 << 20;
 constexpr int kMinEntriesPerSlab = 8;
 constexpr int kDefaultPiece = 64;
 constexpr int kMaxPiece = 512;
-// Below this many bytes per row of B the library schedules nothing unless a threshold is given:
-// with narrow rows the time of a product is set by its short rows (a chain of dependent loads per
-// row that the merge-path kernel hides behind the long rows' streaming gather), and taking the long
-// rows out leaves that chain exposed.  Config 3 (256-byte rows): 653 us without a schedule, 1.0-1.5 ms
-// with one at any threshold, although its pieces read 0.49 GB from HBM instead of 2.4 GB.
+// Below this many bytes per row of B the library schedules nothing unless a threshold is given.  With
+// narrow rows the long rows' half of a product and the short rows' half add up either way, the
+// pieces turn an HBM-bound half into an L2-bound one that is only a third shorter, and the slots and
+// the stepping over scheduled rows in the merge-path kernel cost more than that.  Config 3 (256-byte
+// rows): 0.60 ms without a schedule, 1.0 ms with one, although its pieces read 0.43 GB from HBM
+// instead of 2.1 GB.
 constexpr size_t kMinRowBytesForAuto = 1024;
 // ... and nothing when the scheduled rows together name each row of B fewer than this many times: what the
 // pieces save is the re-use of a slab's rows while it sits in L2, and a row block of a matrix cut across N
