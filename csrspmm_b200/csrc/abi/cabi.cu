@@ -238,11 +238,15 @@ bool on_device(const void* ptr)
 // unsplit product bit for bit.  On the device a panel is stored contiguously (ld = its width).
 constexpr int kMaxPanels = CSRSPMM_B200_MAX_PANELS;
 
-// Column panels of a host round trip over Nd columns: `requested` > 0 asks for that many, else
-// CSRSPMM_HOST_PANELS in the environment (1 = off), else the rule -- a B of 256 MiB and more with
-// Nd >= 256 goes in panels of 128 columns (512-byte segments in the strided host copies), at
-// most eight.  Widths are multiples of 32 columns except possibly the last.  Returns the count
-// and fills first[]/width[] (kMaxPanels entries each) when they are given.
+// Column panels of a host round trip over Nd columns: `requested` > 0 asks for that many equal panels,
+// else CSRSPMM_HOST_PANELS in the environment (1 = off), else the rule -- a B of 256 MiB and more
+// with Nd >= 256 goes in panels of 128 columns (512-byte segments in the strided host copies; wider when
+// that would make more than eight) between a first and a last panel of 64: the first panel's upload and the last panel's download overlap
+// nothing, so they are the short ones, while 256-byte segments copy too slowly to use throughout
+// (config 5 from host memory, one GPU, same box: 217.5 ms this way, 221.1 ms with four panels of 128,
+// 240 ms with eight of 64).
+// Widths are multiples of 32 columns except possibly the last.  Returns the count and fills
+// first[]/width[] (kMaxPanels entries each) when they are given.
 int column_panel_layout(int32_t Kd, int32_t Nd, int requested, int32_t* first, int32_t* width)
 {
     int want = requested;
@@ -250,8 +254,24 @@ int column_panel_layout(int32_t Kd, int32_t Nd, int requested, int32_t* first, i
         if (const char* e = std::getenv("CSRSPMM_HOST_PANELS")) want = std::atoi(e);
     if (want <= 0) {
         const size_t b_bytes = (size_t)Kd * (size_t)Nd * 4;
-        want = (b_bytes >= ((size_t)256 << 20) && Nd >= 256) ? Nd / 128 : 1;
-        if (want > 8) want = 8;
+        if (b_bytes >= ((size_t)256 << 20) && Nd >= 256) {
+            int mid = 128;  // at most eight panels between the first and the last
+            if ((Nd - 128 + mid - 1) / mid > 8) mid = ((Nd - 128 + 7) / 8 + 31) / 32 * 32;
+            int count = 0, c0 = 0;
+            auto put = [&](int w) {
+                if (first) first[count] = c0;
+                if (width) width[count] = w;
+                c0 += w;
+                ++count;
+            };
+            put(64);
+            while (Nd - c0 > mid + 64) put(mid);
+            const int rest = Nd - c0;  // 65 .. mid + 64 columns: all but the last 64 in one panel
+            if (rest > 64) put((rest - 64 + 31) / 32 * 32 < rest ? (rest - 64 + 31) / 32 * 32 : rest);
+            if (Nd - c0 > 0) put(Nd - c0);
+            return count;
+        }
+        want = 1;
     }
     if (want > kMaxPanels) want = kMaxPanels;
     if (want > Nd / 32) want = Nd / 32;  // never narrower than 32 columns

@@ -104,7 +104,7 @@ def sum_over_ranks(value: float, device) -> float:
 def column_panels(Kd: int, Nd: int, panels: int | None = None):
     """[(first column, width)] of the column panels a host round trip is cut into, as the C library
     lays them out.  ``panels`` None applies its rule (a B of 256 MiB or more with Nd >= 256: panels
-    of 128 columns, at most eight; CSRSPMM_HOST_PANELS in the environment overrides); widths are
+    of 128 columns between a first and a last panel of 64; CSRSPMM_HOST_PANELS in the environment overrides); widths are
     multiples of 32 columns except possibly the last."""
     first = np.zeros(16, np.int32)
     width = np.zeros(16, np.int32)

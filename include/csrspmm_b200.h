@@ -136,7 +136,7 @@ int csrspmm_b200_spmm_sync(const csrspmm_b200_args* args, csrspmm_b200_stream_t 
  * row_ptr, col_idx and values may each be DEVICE memory instead (a matrix the caller keeps on the GPU
  * between products, where only B changes): such an array is used in place and not copied.
  * Copies and kernels overlap: a B of 256 MiB or more with Nd >= 256 is processed in column panels
- * of 128 columns (panel q+1 of B arrives and panel q-1 of C leaves while panel q is multiplied;
+ * of 128 columns between a first and a last panel of 64 (panel q+1 of B arrives and panel q-1 of C leaves while panel q is multiplied;
  * CSRSPMM_HOST_PANELS=<n> in the environment sets the number of panels, 1 = none); otherwise a
  * large C goes back in row blocks while the next block is computed.  Either way every element of
  * C is the same sequential sum as in one unsplit product. */
