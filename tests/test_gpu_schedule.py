@@ -176,6 +176,28 @@ def test_prepared_call_with_a_schedule(cuda_lib):
     assert torch.equal(first, out)
 
 
+def test_scheduled_product_replayed_from_a_stream_capture(cuda_lib):
+    """The pieces kernel hands out work from a counter in the call's scratch; the memset that zeroes it is part
+    of the product, so a captured product can be replayed any number of times."""
+    p = skewed(4096, 8192, 128, seed=10)
+    rp, ci, va, B = dev(p.row_ptr), dev(p.col_idx), dev(p.values), dev(p.B)
+    s = ops.Schedule(rp, ci, p.Kd, 128, threshold=16, slab_rows=1024, piece_nnz=32)
+    out = torch.empty(p.M, 128, device="cuda")
+    call = ops.SpmmCall(rp, ci, va, B, out, schedule=s)
+    call()
+    torch.cuda.synchronize()
+    eager = out.clone()
+    g, side = torch.cuda.CUDAGraph(), torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(g, stream=side):
+            call()
+    for _ in range(3):
+        out.fill_(float("nan"))
+        g.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(out, eager)
+
+
 def test_even_rows_keep_the_whole_row_kernel(cuda_lib):
     """With AUTO and a longest row known to be close to the mean, the whole-row kernel is the better choice and
     a schedule is left aside; csrspmm_b200_select_kernel says which way a call will go."""
