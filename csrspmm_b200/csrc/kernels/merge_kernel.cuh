@@ -97,7 +97,8 @@ struct TileRange {
     int il1, jl1;    // the group's end
 };
 
-// Steps 1-3.  Returns false (for every thread of the CTA) when row_ptr is inconsistent.
+// Steps 1-3.  Returns false (for every thread of the CTA) when there is nothing for the CTA to do: row_ptr
+// is inconsistent, or (SKIP) the tile lies inside one scheduled row.
 // SKIP: rows of p.skip_len entries or more belong to the scheduled pieces; they are marked in
 // s.longbits and 32-entry runs that lie wholly inside such a row are not fetched.
 template <class Smem, int G, int TG, int FMT, bool SKIP = false>
@@ -165,6 +166,10 @@ __device__ __forceinline__ bool merge_tile_setup(const SpmmParams& p, Smem& s, T
             }
         }
         __syncthreads();
+        if (r.nrows == 0 && s.is_long(0)) {  // the whole tile lies inside one scheduled row: nothing to do here
+            if (tid == 0) p.carry_row[blockIdx.x] = -1;
+            return false;
+        }
         for (int k0 = tid; k0 < r.nnzt; k0 += kMergeThreads * SB) {
             int c[SB];
             float a[SB];
