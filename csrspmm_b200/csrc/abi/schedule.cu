@@ -126,7 +126,7 @@ cudaError_t launch_sliced_one(const SpmmParams& p, const SlicedParams& q, unsign
 {
     constexpr int G = kPieceShapes[S].G, NV = kPieceShapes[S].NV;
     constexpr int D = VW == 1 ? 16 : kPieceShapes[S].D;
-    auto kern = spmm_sliced_kernel<G, NV, VW, D, FMT, FULL, 2>;
+    auto kern = spmm_sliced_kernel<G, NV, VW, D, FMT, FULL, CSRSPMM_TUNE_SLICED_MINB>;
     const size_t smem = sliced_smem_bytes(G, NV, VW, D, q.pieces_per_group, q.piece_cap);
     static bool configured[64] = {};
     static size_t granted[64] = {};

@@ -28,6 +28,10 @@
 #ifndef CSRSPMM_TUNE_SLICED_PIECES_PER_GROUP
 #define CSRSPMM_TUNE_SLICED_PIECES_PER_GROUP 1
 #endif
+// scheduled pieces: resident CTAs per SM asked of the compiler (caps the registers)
+#ifndef CSRSPMM_TUNE_SLICED_MINB
+#define CSRSPMM_TUNE_SLICED_MINB 2
+#endif
 // scheduled pieces load B with an evict_last policy (1) or plainly (0)
 #ifndef CSRSPMM_TUNE_SLICED_EVICT_LAST
 #define CSRSPMM_TUNE_SLICED_EVICT_LAST 0
