@@ -66,10 +66,12 @@ int env_int(const char* name)
     return (e != nullptr && *e != 0) ? std::atoi(e) : 0;
 }
 
-// Slab of B that should stay in L2 while its pieces run (126 MB of L2, shared with the streams of A,
-// the slots and the other rows' gather).  Measured on config 5 (rows of B of 2 KB): 24 / 32 / 48 /
-// 64 MiB gave 39.2 / 38.9 / 38.9 / 38.9 ms at a threshold of 4096 and 39.0 / 38.6 / 38.5 ms for
-// 32 / 48 / 64 MiB at 2048, against 40.5 ms without a schedule.
+// Slab of B that should stay in L2 while its pieces run.  The 126 MB of L2 are two partitions, one per die, and
+// a line that SMs of both dies read is held in both (tests/cpp/l2_partition_probe.cu measures it), so a slab
+// of 64 MiB that every SM gathers from fills the L2 about once over, next to the streams of A and the slots;
+// the pieces kernel then reads B from HBM about twice (once per die).  Smaller slabs are read once but cut
+// the rows into more pieces, each with a slot of its own; measured on config 5 (rows of B of 2 KB), persistent
+// pieces kernel, threshold 1024: 48 / 64 / 96 MiB gave 36.2 / 36.0 / 36.0 ms, against 40.5 ms without a schedule.
 constexpr size_t kSlabBytes = (size_t)64 << 20;
 // A row is scheduled when it has this many entries per slab on average: each piece costs a slot
 // written and read back (one row of Nd floats each way), so a few entries per piece buy nothing.
